@@ -54,9 +54,9 @@ class KvRequest:
 
 @dataclass(frozen=True)
 class StateRequest:
-    """Fixed-size per-sequence state: one tensor [slots, *shape] of `dtype`."""
+    """Fixed-size per-sequence state: one tensor [slots, *shape] of `dtype` (None: the cache's)."""
     shape: tuple
-    dtype: torch.dtype = torch.float32
+    dtype: torch.dtype | None = torch.float32
 
 
 class _SlotPages:
@@ -156,7 +156,7 @@ class PagedCache:
             if request is None:
                 self.states.append(None)
             else:
-                self.states.append(torch.zeros((max_slots, *request.shape), dtype=request.dtype,
+                self.states.append(torch.zeros((max_slots, *request.shape), dtype=request.dtype or dtype,
                                                device=self.device))
 
     def __del__(self):

@@ -1,9 +1,11 @@
 from .base import ConfigReader, read_config_json
+from .guberax import GuberaxConfig
 from .llama import LlamaConfig
 from .registry import (config_class_for, config_from_dict, known_architectures, load_config,
                        register_architecture)
 
 register_architecture(LlamaConfig.architecture, LlamaConfig)
+register_architecture(GuberaxConfig.architecture, GuberaxConfig)
 
-__all__ = ["ConfigReader", "read_config_json", "LlamaConfig", "config_class_for",
+__all__ = ["ConfigReader", "read_config_json", "LlamaConfig", "GuberaxConfig", "config_class_for",
            "config_from_dict", "known_architectures", "load_config", "register_architecture"]

@@ -29,8 +29,11 @@ def config_class_for(name: str):
 
 
 def config_from_dict(raw: dict, where: str = "config.json"):
-    """Pick the class by `architectures[0]` and parse."""
+    """Pick the class by `architectures[0]` (or, where a configuration names one architecture
+    as a string, by `architecture`) and parse."""
     archs = raw.get("architectures") if isinstance(raw, dict) else None
+    if archs is None and isinstance(raw, dict) and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
         raise FormatError(f"{where}: 'architectures' must be a non-empty list of names")
     return config_class_for(archs[0]).from_dict(raw, where)

@@ -468,6 +468,57 @@ LLMB_EXPORT int llmb_scale(float* x, long long n, float scale, cudaStream_t stre
     return check_launch("scale");
 }
 
+// ----------------------------------------------------------------------------- soft cap in place
+// x = cap * tanh(x / cap) over n 32-bit values (the logits of an architecture that caps them).
+__global__ void softcap_kernel(float* __restrict__ x, long long n, float cap) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) x[i] = cap * tanhf(x[i] / cap);
+}
+
+LLMB_EXPORT int llmb_softcap(float* x, long long n, float cap, cudaStream_t stream) {
+    if (n <= 0) return LLMB_OK;
+    LLMB_REQUIRE(cap > 0.f, "softcap: the cap must be positive");
+    int blocks = (int)((n + 255) / 256 < 148 * 8 ? (n + 255) / 256 : 148 * 8);
+    softcap_kernel<<<blocks, 256, 0, stream>>>(x, n, cap);
+    return check_launch("softcap");
+}
+
+// ----------------------------------------------------------------------------- adding rows into the residual
+// x[t, :] += y[t, :] (both 32-bit): a stream that is added to the residual again between two runs of
+// layers (the embedding output before a repeated pass). With `rows` and `sumsq` the kernel also
+// leaves the next norm's input, as cast_sumsq does. One block per row, the sum in a fixed order.
+__global__ void __launch_bounds__(256)
+add_rows_kernel(float* __restrict__ x, const float* __restrict__ y, int hidden, __nv_bfloat16* __restrict__ rows,
+                float* __restrict__ sumsq) {
+    griddep_launch();
+    griddep_wait();
+    __shared__ float scratch[8];
+    int t = blockIdx.x;
+    float* out = x + (size_t)t * hidden;
+    const float* add = y + (size_t)t * hidden;
+    float sq = 0.f;
+    for (int e = threadIdx.x; e < hidden; e += blockDim.x) {
+        float v = out[e] + add[e];
+        out[e] = v;
+        if (rows) rows[(size_t)t * hidden + e] = __float2bfloat16_rn(v);
+        sq = fmaf(v, v, sq);
+    }
+    if (sumsq) {
+        float total = block_sum_256(sq, scratch);
+        if (threadIdx.x == 0) sumsq[(size_t)t * LLMB_SUMSQ_LD] = total;
+    }
+}
+
+LLMB_EXPORT int llmb_add_rows(float* x, const float* y, int n_rows, int hidden, void* rows, float* sumsq,
+                              cudaStream_t stream) {
+    if (n_rows == 0) return LLMB_OK;
+    LLMB_REQUIRE(n_rows > 0 && hidden > 0, "add_rows: bad sizes");
+    LLMB_REQUIRE((rows != nullptr) == (sumsq != nullptr), "add_rows: give both the bfloat16 rows and the sums, or neither");
+    llmb::launch(add_rows_kernel, n_rows, 256, 0, stream, true, x, y, hidden, (__nv_bfloat16*)rows, sumsq);
+    return check_launch("add_rows");
+}
+
 // ----------------------------------------------------------------------------- gated activation
 // act[t, f] = silu(gu[t, f]) * gu[t, F + f], silu(z) = z / (1 + exp(-z))
 // (apps/engine/kernels/gpu.cu:409-418, apps/engine/src/ops.rs:33-35). The gate
@@ -563,4 +614,6 @@ LLMB_PACKED(llmb_cast_sumsq)
 LLMB_PACKED(llmb_scale_rows)
 LLMB_PACKED(llmb_rope_cache_write)
 LLMB_PACKED(llmb_scale)
+LLMB_PACKED(llmb_softcap)
+LLMB_PACKED(llmb_add_rows)
 LLMB_PACKED(llmb_swiglu)

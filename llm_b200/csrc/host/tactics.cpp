@@ -23,6 +23,8 @@ struct Shape {
     int m = 0, n = 0, k = 0, lda = 0;
     // attention
     int decode = 0, n_heads = 1, n_kv_heads = 1, head_dim = 0, window = 0, packed = 0;
+    // differential attention: head_dim is the size of one map, value_dim the size of a value
+    int value_dim = 0, keep_first = 0;
     // both
     int bf16 = 0;          // operands (and caches) are bfloat16
     int aligned = 1;       // operands start on 16-byte boundaries
@@ -89,6 +91,13 @@ std::string prefill_tc_guard(const Shape& s) {
     return "";
 }
 
+std::string diff_generic_guard(const Shape& s) {
+    if (s.head_dim > LLMB_MAX_HEAD_DIM || s.value_dim > LLMB_MAX_HEAD_DIM)
+        return "map size " + std::to_string(s.head_dim) + " or value size " + std::to_string(s.value_dim) + " exceeds " +
+               std::to_string(LLMB_MAX_HEAD_DIM);
+    return "";
+}
+
 const std::vector<Row>& table(int family) {
     static const std::vector<Row> linear = {
         {"gemm_tc", 30, tc_guard,
@@ -121,7 +130,12 @@ const std::vector<Row>& table(int family) {
          "one block per (token, head), 32-bit arithmetic, any head size up to 256, any group, window and ring; "
          "the only variant of the 32-bit path"},
     };
-    return family == 0 ? linear : attention;
+    static const std::vector<Row> diff_attention = {
+        {"diff_attention_generic", 0, diff_generic_guard,
+         "one block per (token, head), both maps in one pass over the visible keys, 32-bit arithmetic, any sizes "
+         "up to 256, any group, window and kept first tokens; the only variant of the 32-bit path"},
+    };
+    return family == 0 ? linear : family == 1 ? attention : diff_attention;
 }
 
 std::set<std::string>& switched_off() {
@@ -151,16 +165,18 @@ void copy_out(const std::string& text, char* out, int capacity) {
 
 }  // namespace
 
-// family: 0 products, 1 attention. shape: 12 ints {m, n, k, lda, decode, n_heads, n_kv_heads, head_dim,
-// window, packed, bf16, aligned}. name and reasons are filled up to their capacities.
+// family: 0 products, 1 attention, 2 differential attention. shape: 12 ints {m, n, k, lda, decode, n_heads,
+// n_kv_heads, head_dim, window, packed, bf16, aligned}, for family 2 two more {value_dim, keep_first}. name and
+// reasons are filled up to their capacities.
 LLMH_EXPORT int llmh_tactics_choose(int family, const int* shape, char* name, int name_capacity, char* reasons,
                                     int reasons_capacity) {
     return guarded([&] {
-        if (family != 0 && family != 1) throw Failure{LLMH_FORMAT, "unknown kernel family"};
+        if (family < 0 || family > 2) throw Failure{LLMH_FORMAT, "unknown kernel family"};
         Shape s;
         s.m = shape[0]; s.n = shape[1]; s.k = shape[2]; s.lda = shape[3];
         s.decode = shape[4]; s.n_heads = std::max(shape[5], 1); s.n_kv_heads = std::max(shape[6], 1);
         s.head_dim = shape[7]; s.window = shape[8]; s.packed = shape[9]; s.bf16 = shape[10]; s.aligned = shape[11];
+        if (family == 2) { s.value_dim = shape[12]; s.keep_first = shape[13]; }
         std::string why;
         copy_out(choose(family, s, &why), name, name_capacity);
         copy_out(why, reasons, reasons_capacity);
@@ -175,10 +191,10 @@ LLMH_EXPORT void llmh_tactics_set_disabled(const char* name, int disabled) {
 }
 LLMH_EXPORT int llmh_tactics_is_disabled(const char* name) { return switched_off().count(name) ? 1 : 0; }
 
-LLMH_EXPORT int llmh_tactics_rows(int family) { return (family == 0 || family == 1) ? (int)table(family).size() : 0; }
+LLMH_EXPORT int llmh_tactics_rows(int family) { return (family >= 0 && family <= 2) ? (int)table(family).size() : 0; }
 LLMH_EXPORT int llmh_tactics_row(int family, int index, const char** name, int* rank, const char** evidence) {
     return guarded([&] {
-        if ((family != 0 && family != 1) || index < 0 || index >= (int)table(family).size())
+        if (family < 0 || family > 2 || index < 0 || index >= (int)table(family).size())
             throw Failure{LLMH_INVARIANT, "no such row"};
         const Row& row = table(family)[index];
         *name = row.name;

@@ -24,6 +24,8 @@ class DecoderModel:
         for i, item in enumerate(spec.schedule):
             if not 0 <= item.layer < len(self.blocks):
                 raise FormatError(f"schedule entry {i} names layer {item.layer} of {len(self.blocks)}")
+            if getattr(item, "add_embedding", False) and i == 0:
+                raise FormatError("the first schedule entry cannot add the embedding output: it is the stream")
             if item.cache_of is not None and not (
                     0 <= item.cache_of < i and spec.schedule[item.cache_of].cache_of is None):
                 raise FormatError(f"schedule entry {i} reads the cache of entry {item.cache_of}, "
@@ -178,13 +180,24 @@ class DecoderModel:
             block = self.blocks[schedule[position].layer]
             return block.input_emit(ctx, n, self.device) if getattr(block, "chains_norms", False) else None
 
+        def added_before(position):
+            return position < len(schedule) and getattr(schedule[position], "add_embedding", False)
+
         emit = wanted_by(0)
-        x = ops.embed(tokens, self.embedding, scale=getattr(self.spec, "embedding_scale", 1.0), emit=emit)
+        scale = getattr(self.spec, "embedding_scale", 1.0)
+        x = ops.embed(tokens, self.embedding, scale=scale, emit=emit)
+        # the embedding output, for the runs that add it to the stream again (gathered a second time:
+        # every operation of a pass is a launch of this library, so that the pass can be recorded)
+        x0 = ops.embed(tokens, self.embedding, scale=scale) if any(added_before(i) for i in range(len(schedule))) else None
         for entry, item in enumerate(schedule):
             cache_entry = entry if item.cache_of is None else item.cache_of
             block = self.blocks[item.layer]
+            if added_before(entry):
+                emit = wanted_by(entry)
+                ops.add_rows_(x, x0, emit=emit)
             if getattr(block, "chains_norms", False):
-                emit_next = wanted_by(entry + 1)
+                # a run before which the embedding is added gets its norm's input from that addition
+                emit_next = None if added_before(entry + 1) else wanted_by(entry + 1)
                 block.forward(x, ctx, entry, cache_entry, normed=emit, emit_next=emit_next)
                 emit = emit_next
             else:
@@ -196,6 +209,8 @@ class DecoderModel:
         logits = ops.linear(z, self.head, out_dtype=torch.float32)
         if getattr(self.spec, "logit_scale", 1.0) != 1.0:
             ops.scale_(logits, self.spec.logit_scale)
+        if getattr(self.spec, "logit_softcap", 0.0) > 0.0:
+            ops.softcap_(logits, self.spec.logit_softcap)
         return logits
 
 

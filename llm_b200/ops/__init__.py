@@ -344,6 +344,30 @@ def scale_(x, scale: float):
     return x
 
 
+def softcap_(x, cap: float):
+    """x = cap * tanh(x / cap) in place (float32, contiguous)."""
+    _require_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("softcap_: the tensor must be contiguous float32")
+    _call("elementwise", "llmb_softcap", _ptr(x), ctypes.c_longlong(x.numel()), _c_float(cap), _stream())
+    return x
+
+
+def add_rows_(x, y, emit=None):
+    """x += y in place (both contiguous float32 [T, hidden]). With `emit` (an Emit) the sums are also
+    left as bfloat16 rows with the sums of their squares: the next norm's input."""
+    _require_cuda(x, y)
+    if (x.dtype != torch.float32 or y.dtype != torch.float32 or x.shape != y.shape or not x.is_contiguous()
+            or not y.is_contiguous()):
+        raise KernelError("add_rows_: both tensors must be contiguous float32 of one shape")
+    if emit is not None:
+        emit.check(x.shape[0], x.shape[1])
+        emit.parts = 1
+    _call("elementwise", "llmb_add_rows", _ptr(x), _ptr(y), _c_int(x.shape[0]), _c_int(x.shape[1]),
+          _ptr(emit.rows) if emit is not None else None, _ptr(emit.sumsq) if emit is not None else None, _stream())
+    return x
+
+
 def rmsnorm(x, gain, eps, out_dtype, rows=None, out=None):
     """out[r, :] = x[rows[r] or r, :] / sqrt(mean(x^2) + eps) * gain; x and gain float32."""
     _require_cuda(x, gain, rows)
@@ -395,6 +419,51 @@ def rope_cache_write(qkv, rope_table, tok_pos, tok_seq, block_table, ring_pages,
           _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(k_cache), _ptr(v_cache),
           _c_int(n), _c_int(n_heads), _c_int(n_kv_heads), _c_int(head_dim), _c_int(n_rot),
           _c_int(1 if interleaved else 0), _c_int(1 if write_cache else 0), _stream())
+
+
+def conv_rope_cache_write(u, conv_w, state, tok_pos, tok_seq, cu_seqlens, seq_lens, slot_ids, rope_table,
+                          rot_unit, interleaved, q_out, k_width, v_width, block_table, ring_pages, k_cache,
+                          v_cache, write_cache=True, single_tokens=False):
+    """What lies between the q/k/v projection and the attention of a mixer with a short convolution:
+    a causal convolution over time on every channel of `u` [T, Cq + Ck + Cv] (weights `conv_w`
+    float32 [C, taps], or None for no convolution; `state` [slots, taps - 1, C] in u's dtype holds the
+    rows before the step's first token and is brought up to date), then the rotation of every unit of
+    `rot_unit` channels of the query and key parts by `rope_table` [positions, n_rot] (None: no
+    rotation), queries to `q_out` [T, Cq], keys and values into the paged cache
+    (k_cache [pages, Hk, 64, Dk], v_cache [pages, Hv, 64, Dv] with Hk * Dk = Ck, Hv * Dv = Cv).
+    `single_tokens`: every sequence brings exactly one token (the kernel then shifts the state
+    itself; otherwise a second kernel does)."""
+    _require_cuda(u, conv_w, state, tok_pos, tok_seq, cu_seqlens, seq_lens, slot_ids, rope_table, q_out,
+                  block_table, k_cache, v_cache)
+    n, q_width = q_out.shape
+    channels = q_width + k_width + v_width
+    if u.dim() != 2 or u.shape != (n, channels) or u.stride(1) != 1 or not q_out.is_contiguous() or q_out.dtype != u.dtype:
+        raise KernelError(f"conv_rope_cache_write: u {tuple(u.shape)} does not fit [{n}, {q_width} + {k_width} + {v_width}]")
+    taps = 0
+    if conv_w is not None:
+        taps = conv_w.shape[1]
+        if conv_w.dtype != torch.float32 or conv_w.shape[0] != channels or not conv_w.is_contiguous():
+            raise KernelError(f"conv_rope_cache_write: the taps must be contiguous float32 [{channels}, taps]")
+        if taps > 1 and (state is None or state.dtype != u.dtype or tuple(state.shape[1:]) != (taps - 1, channels)
+                         or not state.is_contiguous()):
+            raise KernelError(f"conv_rope_cache_write: the state must be contiguous {u.dtype} [slots, {taps - 1}, {channels}]")
+    n_rot = 0
+    if rope_table is not None:
+        n_rot = rope_table.shape[1]
+        if rope_table.dtype != torch.float32 or not rope_table.is_contiguous():
+            raise KernelError("conv_rope_cache_write: the table of angles must be contiguous float32")
+    if k_cache.dtype != u.dtype or v_cache.dtype != u.dtype or not k_cache.is_contiguous() or not v_cache.is_contiguous():
+        raise KernelError("conv_rope_cache_write: the cache must be contiguous and of the projection's dtype")
+    kernels = 2 if (conv_w is not None and taps > 1 and not single_tokens) else 1
+    _call("short_conv", "llmb_conv_rope_cache_write", _ptr(u), _c_int(u.stride(0)), _c_int(_code(u.dtype)),
+          _ptr(conv_w), _c_int(taps), _ptr(state), _ptr(tok_pos), _ptr(tok_seq), _ptr(cu_seqlens), _ptr(seq_lens),
+          _ptr(slot_ids), _ptr(rope_table), _c_int(n_rot), _c_int(rot_unit), _c_int(1 if interleaved else 0),
+          _ptr(q_out), _c_int(q_width), _c_int(k_width), _c_int(v_width), _ptr(block_table),
+          _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(k_cache), _c_int(k_cache.shape[1]),
+          _c_int(k_cache.shape[3]), _ptr(v_cache), _c_int(v_cache.shape[1]), _c_int(v_cache.shape[3]),
+          _c_int(1 if write_cache else 0), _c_int(n), _c_int(cu_seqlens.numel() - 1),
+          _c_int(1 if single_tokens else 0), _stream(), kernels=kernels)
+    return q_out
 
 
 # ----------------------------------------------------------------------------- matrix product
@@ -717,6 +786,47 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
     return out
 
 
+def diff_attention_replay_key(step, spec):
+    """What the launches of a differential attention depend on beyond the token and sequence counts
+    (Part.replay_key): the kernels size their grids by the most new tokens of a sequence."""
+    if step.decode:
+        return (True,)
+    return (False, max(step.new_counts))
+
+
+def diff_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads, n_kv_heads, dim,
+                   vdim, scale, window, keep_first, lam, eps, out_scale, head_norm=True, out=None, decode=False,
+                   seq_lens=None, max_len=0, cu_seqlens=None, max_new=0, seq_order=None):
+    """Differential attention of the new tokens' queries q [T, H * 2 * dim] (per head: map 1, map 2)
+    over the paged cache (keys [pages, G, 64, 2 * dim], values [pages, G, 64, vdim]), which already
+    holds the new tokens. Per head: o = a1 - lam * a2 with a1, a2 the two maps' softmax attentions
+    over the same values; then (with `head_norm`) o / sqrt(mean(o^2) + eps); times out_scale. A
+    query at position p sees key j <= p if window == 0, p - j < window or j < keep_first.
+    Returns [T, H * vdim] in q's dtype."""
+    _require_cuda(q, k_cache, v_cache, block_table, tok_pos, tok_seq)
+    n = q.shape[0]
+    if q.shape[1] != n_heads * 2 * dim or q.stride(1) != 1:
+        raise KernelError(f"diff_attention: q {tuple(q.shape)} is not [T, {n_heads} * 2 * {dim}]")
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, 2 * dim) or tuple(v_cache.shape[1:]) != (n_kv_heads, PAGE, vdim):
+        raise KernelError(f"diff_attention: the cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} does not fit "
+                          f"{n_kv_heads} heads of 2 * {dim} and {vdim}")
+    _check_out(out, (n, n_heads * vdim), q.dtype, "diff_attention")
+    if out is None:
+        out = torch.empty((n, n_heads * vdim), dtype=q.dtype, device=q.device)
+    variant = tactics.choose_diff_attention(decode, q.dtype, n_heads, n_kv_heads, dim, vdim, window, keep_first,
+                                            cu_seqlens is not None and seq_lens is not None,
+                                            q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
+    if variant == "diff_attention_generic":
+        _call("diff_attention", "llmb_diff_attention_generic", _ptr(q), _c_int(q.stride(0)), _ptr(k_cache),
+              _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(tok_pos),
+              _ptr(tok_seq), _ptr(out), _c_int(out.stride(0)), _c_int(_code(q.dtype)), _c_int(n), _c_int(n_heads),
+              _c_int(n_kv_heads), _c_int(dim), _c_int(vdim), _c_float(scale), _c_int(window), _c_int(keep_first),
+              _c_float(lam), _c_float(eps), _c_float(out_scale), _c_int(1 if head_norm else 0), _stream())
+    else:
+        raise KernelError(f"diff_attention: no kernel named {variant}")
+    return out
+
+
 # ----------------------------------------------------------------------------- sampling
 
 def argmax_rows(logits, out=None):
@@ -755,5 +865,6 @@ def required_libraries() -> list:
 
 
 __all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "random_normal_", "begin_recording", "end_recording", "RecordedPass", "scratch_generation", "Emit", "FoldedNorm", "RopeWrite", "cast_sumsq", "SUMSQ_LD", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
+           "softcap_", "add_rows_", "conv_rope_cache_write", "diff_attention",
            "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "check_device_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

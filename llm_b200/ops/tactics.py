@@ -21,7 +21,7 @@ import torch
 
 from .. import native
 
-_FAMILY = {"linear": 0, "attention": 1}
+_FAMILY = {"linear": 0, "attention": 1, "diff_attention": 2}
 
 
 @dataclass(frozen=True)
@@ -69,10 +69,12 @@ def is_disabled(name: str) -> bool:
 
 
 def _choose(family: str, m=0, n=0, k=0, lda=0, decode=False, n_heads=1, n_kv_heads=1, head_dim=0,
-            window=0, packed=False, aligned=True, in_dtype=None, out_dtype=None, dtype=None):
+            window=0, packed=False, aligned=True, in_dtype=None, out_dtype=None, dtype=None, value_dim=0,
+            keep_first=0):
     bf16 = (in_dtype if in_dtype is not None else dtype) == torch.bfloat16
-    shape = (c_int * 12)(int(m), int(n), int(k), int(lda), int(bool(decode)), int(n_heads), int(n_kv_heads),
-                         int(head_dim), int(window), int(bool(packed)), int(bf16), int(bool(aligned)))
+    shape = (c_int * 14)(int(m), int(n), int(k), int(lda), int(bool(decode)), int(n_heads), int(n_kv_heads),
+                         int(head_dim), int(window), int(bool(packed)), int(bf16), int(bool(aligned)),
+                         int(value_dim), int(keep_first))
     name, reasons = ctypes.create_string_buffer(64), ctypes.create_string_buffer(2048)
     native.check(native.lib().llmh_tactics_choose(_FAMILY[family], shape, name, 64, reasons, 2048))
     return name.value.decode(), reasons.value.decode()
@@ -97,6 +99,19 @@ def choose_attention(decode, dtype, n_heads, n_kv_heads, head_dim, window, packe
         name = _chosen[key] = _choose("attention", decode=decode, dtype=dtype, n_heads=n_heads,
                                       n_kv_heads=n_kv_heads, head_dim=head_dim, window=window,
                                       packed=packed, aligned=aligned)[0]
+    return name
+
+
+def choose_diff_attention(decode, dtype, n_heads, n_kv_heads, head_dim, value_dim, window, keep_first,
+                          packed=False, aligned=True) -> str:
+    """The variant for a differential attention whose maps have `head_dim` elements."""
+    key = ("diff_attention", decode, dtype, n_heads, n_kv_heads, head_dim, value_dim, window, keep_first, packed,
+           aligned)
+    name = _chosen.get(key)
+    if name is None:
+        name = _chosen[key] = _choose("diff_attention", decode=decode, dtype=dtype, n_heads=n_heads,
+                                      n_kv_heads=n_kv_heads, head_dim=head_dim, value_dim=value_dim, window=window,
+                                      keep_first=keep_first, packed=packed, aligned=aligned)[0]
     return name
 
 

@@ -6,7 +6,8 @@ import os
 import torch
 
 from .. import ops
-from .base import (Block, build_feed_forward, build_mixer, build_norm, register_block)
+from ..errors import Unsupported
+from .base import (Block, Part, build_feed_forward, build_mixer, build_norm, register_block)
 
 # LLMB_NO_FUSION=1: every norm stays a kernel of its own (for comparisons)
 FOLD_NORMS = os.environ.get("LLMB_NO_FUSION", "0") in ("", "0")
@@ -169,3 +170,135 @@ class PreNormBlock(Block):
 
 
 register_block("pre_norm", PreNormBlock)
+
+
+class ParallelBlock(Block):
+    """x += mixer(norm(x)) + feed_forward(norm(x)): one norm whose output both parts read; both
+    add into the 32-bit residual stream. The feed-forward may be absent.
+
+    In bfloat16 runs the norm is folded into both parts where both offer it (each multiplies the
+    gain into its own first matrix; both products read the same bfloat16 rows and sums of squares
+    that the last update of the stream left), and the block's last product leaves the same for
+    the block that runs next."""
+
+    chains_norms = True
+
+    def __init__(self, spec):
+        self.spec = spec
+        self.norm = build_norm(spec.norm)
+        self.mixer = build_mixer(spec.mixer)
+        self.feed_forward = build_feed_forward(spec.feed_forward) if spec.feed_forward is not None else None
+        self.folded = False
+
+    @property
+    def parts(self):
+        return tuple(p for p in (self.norm, self.mixer, self.feed_forward) if p is not None)
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self.parts)
+
+    @property
+    def libraries(self):
+        return tuple(lib for p in self.parts for lib in p.libraries)
+
+    def parameters(self):
+        out = {}
+        for p in self.parts:
+            out.update(p.parameters())
+        return out
+
+    def bind(self, tensors, dtype, device):
+        for p in self.parts:
+            p.bind(tensors, dtype, device)
+        # all readers of the norm fold it, or none does (a part's weights change when it folds)
+        self.folded = False
+        if FOLD_NORMS and dtype == torch.bfloat16 and getattr(self.norm, "foldable", False):
+            readers = [p for p in (self.mixer, self.feed_forward) if p is not None]
+            if all(type(p).fold_input_norm is not Part.fold_input_norm for p in readers) \
+                    and self.norm.spec.size % 8 == 0:
+                answers = [bool(p.fold_input_norm(self.norm.gain)) for p in readers]
+                if not all(answers):
+                    if any(answers):
+                        raise Unsupported("a parallel block whose parts do not agree on folding their norm")
+                else:
+                    self.folded = True
+
+    def replay_key(self, step):
+        keys = [p.replay_key(step) for p in self.parts]
+        return None if any(k is None for k in keys) else tuple(keys)
+
+    def input_emit(self, ctx, n_tokens: int, device):
+        if not self.folded:
+            return None
+        hidden = self.spec.norm.size
+        rows = ctx.scratch("h_block", (n_tokens, hidden), torch.bfloat16)
+        sums = ctx.scratch("s_block", (n_tokens, ops.SUMSQ_LD), torch.float32)
+        if rows is None or sums is None:
+            rows = torch.empty((n_tokens, hidden), dtype=torch.bfloat16, device=device)
+            sums = torch.empty((n_tokens, ops.SUMSQ_LD), dtype=torch.float32, device=device)
+        return ops.Emit(rows, sums)
+
+    def prepare(self, max_positions, device):
+        for p in self.parts:
+            p.prepare(max_positions, device)
+
+    def weights(self):
+        return [w for p in self.parts for w in p.weights()]
+
+    def kernel_shapes(self, dtype, token_counts):
+        return [shape for p in self.parts for shape in p.kernel_shapes(dtype, token_counts)]
+
+    def scratch_requests(self, n_tokens, dtype):
+        """The norm's output (or, folded, its input: bfloat16 rows and sums of squares, which the
+        block before wrote and both parts read) lives through the whole block; this block's last
+        product, which reads neither, writes the next block's into the same place."""
+        from ..engine.workspace import BufferRequest
+        hidden = self.spec.norm.size
+        mixer = self.mixer.scratch_requests(n_tokens, dtype)
+        ffn = self.feed_forward.scratch_requests(n_tokens, dtype) if self.feed_forward is not None else []
+        mixer_end = 1 + max([r.last_use for r in mixer] + [0])
+        ffn_start = mixer_end + 1
+        ffn_end = ffn_start + max([r.last_use for r in ffn] + [0])
+        sums = (n_tokens, ops.SUMSQ_LD)
+        if self.folded:
+            out = [BufferRequest("h_block", (n_tokens, hidden), torch.bfloat16, 0, ffn_end + 1),
+                   BufferRequest("s_block", sums, torch.float32, 0, ffn_end + 1)]
+        else:
+            out = [BufferRequest("h_block", (n_tokens, hidden), dtype, 0, ffn_end)]
+        out += [r.shifted(1, "mixer.") for r in mixer]
+        out += [r.shifted(ffn_start, "ffn.") for r in ffn]
+        return out
+
+    def forward(self, x, ctx, entry, cache_entry, normed=None, emit_next=None):
+        views = ctx.workspace
+        n = x.shape[0]
+
+        def prefixed(prefix):
+            if views is not None:
+                views.prefix = prefix
+
+        if self.folded:
+            if normed is None:
+                normed = ops.cast_sumsq(x, self.input_emit(ctx, n, x.device))
+            h = ops.FoldedNorm(normed.rows, normed.sumsq, normed.parts, self.spec.norm.eps, self.spec.norm.size)
+        else:
+            h = self.norm.forward(x, ctx.dtype, out=ctx.scratch("h_block", tuple(x.shape), ctx.dtype))
+        last = self.feed_forward if self.feed_forward is not None else self.mixer
+        prefixed("mixer.")
+        if last is self.mixer and emit_next is not None and self.mixer.emits:
+            self.mixer.forward(h, ctx, entry, cache_entry, x, emit=emit_next)
+        else:
+            self.mixer.forward(h, ctx, entry, cache_entry, x)
+        if self.feed_forward is not None:
+            prefixed("ffn.")
+            if emit_next is not None and self.feed_forward.emits:
+                self.feed_forward.forward(h, ctx, x, emit=emit_next)
+            else:
+                self.feed_forward.forward(h, ctx, x)
+        prefixed("")
+        if emit_next is not None and not last.emits:
+            ops.cast_sumsq(x, emit_next)
+
+
+register_block("parallel", ParallelBlock)

@@ -8,7 +8,8 @@ from .base import Norm, register_norm, to_float32
 
 class RmsNorm(Norm):
     """x / sqrt(mean(x^2) + eps) * weight, the norm of MythEclipse/llm
-    (apps/engine/src/ops.rs:4-12). The weight is held in 32-bit."""
+    (apps/engine/src/ops.rs:4-12). The weight is held in 32-bit. A spec with `unit_offset`
+    stores its weight around zero: the gain is then 1 + weight (added in 32-bit at bind)."""
     graph_safe = True
     libraries = ("elementwise",)
     #: y = x / sqrt(mean(x^2) + eps) * gain: a part behind this norm may fold it (Part.fold_input_norm)
@@ -19,10 +20,13 @@ class RmsNorm(Norm):
         self.gain = None
 
     def parameters(self):
-        return {self.spec.weight: ParamSpec((self.spec.size,), "gain")}
+        role = "gain_offset" if getattr(self.spec, "unit_offset", False) else "gain"
+        return {self.spec.weight: ParamSpec((self.spec.size,), role)}
 
     def bind(self, tensors, dtype, device):
         self.gain = to_float32(tensors[self.spec.weight], device)
+        if getattr(self.spec, "unit_offset", False):
+            self.gain = (self.gain + 1.0).contiguous()
 
     def replay_key(self, step):
         return ()

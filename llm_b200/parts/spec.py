@@ -22,6 +22,7 @@ class NormSpec:
     eps: float
     weight: str                      # tensor name
     kind: str = "rmsnorm"
+    unit_offset: bool = False        # the stored weight lies around zero: the gain is 1 + weight
 
 
 @dataclass(frozen=True)
@@ -59,6 +60,31 @@ class AttentionSpec:
 
 
 @dataclass(frozen=True)
+class DiffAttentionSpec:
+    """Differential attention: every query head has two maps, each a softmax attention of its own
+    over the same values; a head's result is map 1 minus lambda times map 2, divided by its root
+    mean square and multiplied by 1 - diff. lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff."""
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int                    # query / key size of ONE map
+    value_dim: int
+    scale: float                     # multiplies q.k
+    window: int                      # 0: every earlier key; w > 0: keys less than w positions back ...
+    keep_first: int                  # ... and the sequence's first keep_first keys
+    conv_taps: int                   # taps of the causal convolution behind q, k, v (0: none)
+    diff: float                      # lambda's constant term; the result is scaled by 1 - diff
+    eps: float                       # of the head's norm
+    position: Optional[PositionSpec]
+    names: tuple                     # sorted (role, tensor name): q, k, v, o, lq1, lk1, lq2, lk2 (+ q_conv, k_conv, v_conv)
+    kind: str = "diff_attention"
+
+    @property
+    def tensor(self):
+        return dict(self.names)
+
+
+@dataclass(frozen=True)
 class GatedMlpSpec:
     hidden: int
     intermediate: int
@@ -82,11 +108,24 @@ class BlockSpec:
 
 
 @dataclass(frozen=True)
+class ParallelBlockSpec:
+    """x += mixer(norm(x)) + feed_forward(norm(x)): one norm, both parts read its output.
+    `feed_forward` may be None (a layer that only mixes)."""
+    norm: object
+    mixer: object
+    feed_forward: object
+    kind: str = "parallel"
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One run of a layer. `cache_of` names an earlier schedule entry whose
-    keys and values this run reads instead of writing its own."""
+    keys and values this run reads instead of writing its own. With `add_embedding` the
+    embedding output (the stream as it was before the first run) is added to the stream
+    right before this run."""
     layer: int
     cache_of: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)
@@ -103,6 +142,7 @@ class ModelSpec:
     stop_tokens: tuple = field(default_factory=tuple)
     embedding_scale: float = 1.0     # multiplies the embedded tokens
     logit_scale: float = 1.0         # multiplies the logits
+    logit_softcap: float = 0.0       # c > 0: logits <- c * tanh(logits / c), after the scale
 
 
 def names(**roles) -> tuple:

@@ -45,7 +45,8 @@ def random_tensors(expected: dict, seed: int, dtype=torch.bfloat16, std: float =
     name, its index in the tensor), not on the order, on the other tensors or on the
     device that makes it: a model made on the GPU and one written to a folder on the CPU
     from the same seed are the same model. Matrices and biases are N(0, std); gains are
-    1 + N(0, gain_noise). Values are drawn in 32-bit and rounded once to `dtype`."""
+    1 + N(0, gain_noise) (N(0, gain_noise) where the gain is stored as an offset from 1); the taps of a
+    short convolution are N(0, 1 / taps). Values are drawn in 32-bit and rounded once to `dtype`."""
     out = {}
     for name in sorted(expected):
         spec = expected[name]
@@ -55,6 +56,10 @@ def random_tensors(expected: dict, seed: int, dtype=torch.bfloat16, std: float =
         tensor = torch.empty(spec.shape, dtype=dtype, device=device)
         if spec.role == "gain":
             normal_(tensor, tensor_key(seed, name), 1.0, gain_noise)
+        elif spec.role == "gain_offset":                     # a norm's weight that is stored around zero
+            normal_(tensor, tensor_key(seed, name), 0.0, gain_noise)
+        elif spec.role == "taps":                            # a short convolution: taps of the order of 1 / taps
+            normal_(tensor, tensor_key(seed, name), 0.0, 1.0 / max(spec.shape[-1], 1))
         else:
             normal_(tensor, tensor_key(seed, name), 0.0, std)
         out[name] = tensor

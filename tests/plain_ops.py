@@ -144,6 +144,93 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
     return result.to(qkv.dtype)
 
 
+def softcap_(x, cap):
+    x.copy_(cap * torch.tanh(x / cap))
+    return x
+
+
+def add_rows_(x, y, emit=None):
+    x += y
+    if emit is not None:
+        cast_sumsq(x, emit)
+    return x
+
+
+def conv_rope_cache_write(u, conv_w, state, tok_pos, tok_seq, cu_seqlens, seq_lens, slot_ids, rope_table,
+                          rot_unit, interleaved, q_out, k_width, v_width, block_table, ring_pages, k_cache,
+                          v_cache, write_cache=True, single_tokens=False):
+    """Sequence by sequence: the rows before the step's first token come from the state, the
+    convolution is a plain sum over taps, then every unit of `rot_unit` channels of q and k rotates."""
+    n, q_width = q_out.shape
+    if n == 0:
+        return q_out
+    y = torch.empty((n, u.shape[1]), dtype=torch.float32, device=u.device)
+    cu = cu_seqlens.tolist()
+    for b in range(len(cu) - 1):
+        first, last = cu[b], cu[b + 1]
+        rows = u[first:last].to(torch.float32)
+        if conv_w is None:
+            y[first:last] = rows
+            continue
+        taps = conv_w.shape[1]
+        if taps > 1:
+            slot = int(slot_ids[b])
+            history = torch.cat([state[slot].to(torch.float32), rows])
+            state[slot] = history[-(taps - 1):].to(state.dtype)
+        else:
+            history = rows
+        count = last - first
+        total = torch.zeros_like(rows)
+        for j in range(taps):
+            total += conv_w[:, j].to(torch.float32)[None, :] * history[j:j + count]
+        y[first:last] = total
+    pos = tok_pos.long()
+    k_end = q_width + k_width
+    q = y[:, :q_width].reshape(n, -1, rot_unit)
+    k = y[:, q_width:k_end].reshape(n, -1, rot_unit)
+    if rope_table is not None:
+        half = rope_table.shape[1] // 2
+        cos, sin = rope_table[pos, :half], rope_table[pos, half:]
+        q = _rotate(q, cos, sin, interleaved)
+        k = _rotate(k, cos, sin, interleaved)
+    q_out.copy_(q.reshape(n, q_width).to(q_out.dtype))
+    if write_cache:
+        pages = block_table.long()[tok_seq.long(), (pos // PAGE) % ring_pages]
+        rows = pos % PAGE
+        k_cache[pages, :, rows, :] = k.reshape(n, k_cache.shape[1], k_cache.shape[3]).to(k_cache.dtype)
+        v_cache[pages, :, rows, :] = y[:, k_end:].reshape(n, v_cache.shape[1], v_cache.shape[3]).to(v_cache.dtype)
+    return q_out
+
+
+def diff_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads, n_kv_heads, dim,
+                   vdim, scale, window, keep_first, lam, eps, out_scale, head_norm=True, out=None, decode=False,
+                   seq_lens=None, max_len=0, cu_seqlens=None, max_new=0, seq_order=None):
+    n = q.shape[0]
+    result = torch.zeros((n, n_heads * vdim), dtype=torch.float32, device=q.device)
+    group = n_heads // n_kv_heads
+    table = block_table.long()
+    for t in range(n):
+        pos, b = int(tok_pos[t]), int(tok_seq[t])
+        js = torch.arange(0, pos + 1, device=q.device)
+        if window > 0:
+            js = js[(pos - js < window) | (js < keep_first)]
+        pages = table[b, (js // PAGE) % ring_pages]
+        keys = k_cache[pages, :, js % PAGE, :].to(torch.float32)        # [n_keys, G, 2 * dim]
+        vals = v_cache[pages, :, js % PAGE, :].to(torch.float32)        # [n_keys, G, vdim]
+        maps = q[t].to(torch.float32).view(n_heads, 2, dim)
+        for h in range(n_heads):
+            g = h // group
+            a = []
+            for m in range(2):
+                scores = (keys[:, g, m * dim:(m + 1) * dim] @ maps[h, m]) * scale
+                a.append(torch.softmax(scores, dim=0) @ vals[:, g, :])
+            o = a[0] - lam * a[1]
+            if head_norm:
+                o = o / torch.sqrt((o * o).mean() + eps)
+            result[t, h * vdim:(h + 1) * vdim] = o * out_scale
+    return result.to(q.dtype)
+
+
 def argmax_rows(logits, out=None):
     best = logits.max(dim=1, keepdim=True).values
     first = (logits == best).to(torch.int32).argmax(dim=1)
@@ -262,6 +349,8 @@ def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, sta
 
 OPS = {"embed": embed, "scale_": scale_, "cast_sumsq": cast_sumsq, "rmsnorm": rmsnorm, "swiglu": swiglu, "linear": linear,
        "rope_cache_write": rope_cache_write, "attention": attention, "argmax_rows": argmax_rows,
+       "softcap_": softcap_, "add_rows_": add_rows_, "conv_rope_cache_write": conv_rope_cache_write,
+       "diff_attention": diff_attention,
        "sample_rows": sample_rows}
 
 
