@@ -98,6 +98,33 @@ std::string diff_generic_guard(const Shape& s) {
     return "";
 }
 
+bool diff_tc_shape(int dim, int vdim) {
+#define X(DK, DV) if (dim == DK && vdim == DV) return true;
+    LLMB_DIFF_SHAPES(X)
+#undef X
+    return false;
+}
+
+std::string diff_tc_guard(const Shape& s) {
+    if (!s.bf16) return "bfloat16 caches only";
+    if (!diff_tc_shape(s.head_dim, s.value_dim))
+        return "map size " + std::to_string(s.head_dim) + " with value size " + std::to_string(s.value_dim) +
+               " (served: 32/32, 32/64, 48/96, 64/64, 64/128, 128/128)";
+    if (!s.aligned) return "the queries' rows are not 16-byte aligned";
+    return "";
+}
+
+std::string diff_decode_guard(const Shape& s) {
+    if (!s.decode) return "serves steps in which every sequence brings one token";
+    if (s.n_heads / s.n_kv_heads > 8) return "group of " + std::to_string(s.n_heads / s.n_kv_heads) + " query heads exceeds 8";
+    return diff_tc_guard(s);
+}
+
+std::string diff_prefill_guard(const Shape& s) {
+    if (!s.packed) return "needs the packed batch description (cu_seqlens and seq_lens)";
+    return diff_tc_guard(s);
+}
+
 const std::vector<Row>& table(int family) {
     static const std::vector<Row> linear = {
         {"gemm_tc", 30, tc_guard,
@@ -131,6 +158,14 @@ const std::vector<Row>& table(int family) {
          "the only variant of the 32-bit path"},
     };
     static const std::vector<Row> diff_attention = {
+        {"diff_attention_decode", 20, diff_decode_guard,
+         "split-KV decode: the pages a query sees (kept first tokens, then the window) through shared memory with "
+         "cp.async, the group's heads as tile rows 0-7 (map 1) and 8-15 (map 2) of mma.sync tiles, so that one P V "
+         "product serves both maps; the merge forms the difference, the head's norm and the scale"},
+        {"diff_attention_prefill", 10, diff_prefill_guard,
+         "flash attention over the paged cache for steps with several new tokens a sequence: 64-query tiles, map 1 "
+         "on four warps and map 2 on four more over the same pages of keys and values, mma.sync, online softmax, only "
+         "the pages the tile's windows reach; difference, head norm and scale in the epilogue"},
         {"diff_attention_generic", 0, diff_generic_guard,
          "one block per (token, head), both maps in one pass over the visible keys, 32-bit arithmetic, any sizes "
          "up to 256, any group, window and kept first tokens; the only variant of the 32-bit path"},

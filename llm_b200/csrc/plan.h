@@ -7,3 +7,5 @@
 #define LLMB_GLU_BLOCK 16       // gate and up rows alternate in blocks of this many rows where the
                                 // gated activation runs in the product's epilogue
 #define LLMB_MAX_HEAD_DIM 256   // largest head size any attention kernel takes
+// The (map size, value size) pairs the tensor-core kernels of the differential attention are built for.
+#define LLMB_DIFF_SHAPES(X) X(32, 32) X(32, 64) X(48, 96) X(64, 64) X(64, 128) X(128, 128)

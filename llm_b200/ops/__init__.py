@@ -25,7 +25,7 @@ from .build import all_sources, ensure_built, load_library
 
 PAGE = native.plan_constant("page")              # positions per cache page (csrc/plan.h)
 BFLOAT16_ONLY = ("gemm_tc", "gemm_skinny", "attention_decode", "attention_prefill",
-                 "attention_prefill_tc")
+                 "attention_prefill_tc")     # (diff_attention holds the 32-bit kernel too)
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
 _c_int, _c_float, _c_void = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
@@ -786,11 +786,21 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
     return out
 
 
+def diff_decode_splits(n_seqs: int, n_kv_heads: int, max_len: int, window: int, keep_first: int) -> int:
+    """Slices of the decode kernel of the differential attention: `decode_splits` for the keys a query
+    sees at most (with a window: the window, a page of slack, and the pages of the kept first
+    tokens)."""
+    seen = max_len
+    if window > 0:
+        seen = min(max_len, window + PAGE + (((keep_first + PAGE - 1) // PAGE) * PAGE if keep_first else 0))
+    return decode_splits(n_seqs, n_kv_heads, seen)
+
+
 def diff_attention_replay_key(step, spec):
     """What the launches of a differential attention depend on beyond the token and sequence counts
-    (Part.replay_key): the kernels size their grids by the most new tokens of a sequence."""
+    (Part.replay_key): the most new tokens of a sequence (prefill grids), the slices (decode)."""
     if step.decode:
-        return (True,)
+        return (True, diff_decode_splits(step.n_seqs, spec.n_kv_heads, step.max_len, spec.window, spec.keep_first))
     return (False, max(step.new_counts))
 
 
@@ -816,7 +826,31 @@ def diff_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_se
     variant = tactics.choose_diff_attention(decode, q.dtype, n_heads, n_kv_heads, dim, vdim, window, keep_first,
                                             cu_seqlens is not None and seq_lens is not None,
                                             q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0)
-    if variant == "diff_attention_generic":
+    if variant == "diff_attention_prefill":
+        _call("diff_attention", "llmb_diff_attention_prefill", _ptr(q), _c_int(q.stride(0)), _ptr(k_cache),
+              _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(cu_seqlens),
+              _ptr(seq_lens), _ptr(out), _c_int(out.stride(0)), _c_int(cu_seqlens.numel() - 1), _c_int(max_new),
+              _c_int(n_heads), _c_int(n_kv_heads), _c_int(dim), _c_int(vdim), _c_float(scale), _c_int(window),
+              _c_int(keep_first), _c_float(lam), _c_float(eps), _c_float(out_scale), _c_int(1 if head_norm else 0),
+              _stream())
+    elif variant == "diff_attention_decode":
+        splits = diff_decode_splits(n, n_kv_heads, max_len, window, keep_first)
+        need = n * n_heads * 2 * splits * (vdim + 2)
+        scratch = _attention_scratch.get(q.device)
+        if scratch is None or scratch.numel() < need:
+            if scratch is not None:
+                global _scratch_generation
+                _retired.append(scratch)
+                _scratch_generation += 1
+            scratch = torch.empty(max(need, 1 << 23), dtype=torch.float32, device=q.device)
+            _attention_scratch[q.device] = scratch
+        _call("diff_attention", "llmb_diff_attention_decode", _ptr(q), _c_int(q.stride(0)), _ptr(k_cache),
+              _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(seq_lens),
+              _ptr(seq_order), _ptr(out), _c_int(out.stride(0)), _ptr(scratch), ctypes.c_longlong(scratch.numel()),
+              _c_int(n), _c_int(n_heads), _c_int(n_kv_heads), _c_int(dim), _c_int(vdim), _c_float(scale),
+              _c_int(window), _c_int(keep_first), _c_float(lam), _c_float(eps), _c_float(out_scale),
+              _c_int(1 if head_norm else 0), _c_int(splits), _stream(), kernels=2 if splits > 1 else 1)
+    elif variant == "diff_attention_generic":
         _call("diff_attention", "llmb_diff_attention_generic", _ptr(q), _c_int(q.stride(0)), _ptr(k_cache),
               _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(tok_pos),
               _ptr(tok_seq), _ptr(out), _c_int(out.stride(0)), _c_int(_code(q.dtype)), _c_int(n), _c_int(n_heads),

@@ -217,17 +217,14 @@ def diff_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_se
         pages = table[b, (js // PAGE) % ring_pages]
         keys = k_cache[pages, :, js % PAGE, :].to(torch.float32)        # [n_keys, G, 2 * dim]
         vals = v_cache[pages, :, js % PAGE, :].to(torch.float32)        # [n_keys, G, vdim]
-        maps = q[t].to(torch.float32).view(n_heads, 2, dim)
-        for h in range(n_heads):
-            g = h // group
-            a = []
-            for m in range(2):
-                scores = (keys[:, g, m * dim:(m + 1) * dim] @ maps[h, m]) * scale
-                a.append(torch.softmax(scores, dim=0) @ vals[:, g, :])
-            o = a[0] - lam * a[1]
-            if head_norm:
-                o = o / torch.sqrt((o * o).mean() + eps)
-            result[t, h * vdim:(h + 1) * vdim] = o * out_scale
+        maps = q[t].to(torch.float32).view(n_kv_heads, group, 2, dim)
+        split_keys = keys.view(-1, n_kv_heads, 2, dim)
+        scores = torch.einsum("ghmd,jgmd->ghmj", maps, split_keys) * scale       # per kv head, head of its group, map
+        a = torch.einsum("ghmj,jgv->ghmv", torch.softmax(scores, dim=-1), vals)
+        o = a[:, :, 0] - lam * a[:, :, 1]                                         # [G, group, vdim]
+        if head_norm:
+            o = o / torch.sqrt((o * o).mean(dim=-1, keepdim=True) + eps)
+        result[t] = (o * out_scale).reshape(-1)
     return result.to(q.dtype)
 
 

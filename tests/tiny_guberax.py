@@ -47,18 +47,18 @@ GUB_P = {
     ],
 }
 
-# Q: sizes that the 16-byte kernels take (multiples of 8 and 16), window wider than a page, the
+# Q: sizes that the tensor-core kernels take, windows wider and narrower than a page, the
 # repeated range from layer 0, no soft cap
 GUB_Q = {
     "architecture": "Guberax", "vocab": 320, "width": 128, "norm": {"eps": 1e-6},
     "loop": {"start": 0, "stop": 2, "times": 2},
     "layers": [
-        _layer(_mixer(4, 1, 32, 48, conv=4, diff=0.3, mask={"size": 70, "keep_first": 3},
-                      rot={"base": 500000.0, "dims": 16, "scaling": SCALED}), 192),
-        _layer(_mixer(4, 2, 32, 48, conv=4, diff=0.3, mask={"size": 70, "keep_first": 3},
-                      rot={"base": 500000.0, "dims": 32}), 192),
+        _layer(_mixer(4, 1, 32, 32, conv=4, diff=0.35, mask={"size": 70, "keep_first": 3},
+                      rot={"base": 200000.0, "dims": 16, "scaling": SCALED}), 192),
+        _layer(_mixer(4, 2, 32, 64, conv=3, diff=0.35, mask={"size": 70, "keep_first": 3},
+                      rot={"base": 200000.0, "dims": 32}), 192),
         _layer(_mixer(2, 2, 64, 64, conv=4, diff=0.2, mask={"size": 33, "keep_first": 1},
-                      rot={"base": 500000.0, "dims": 64}), 192),
+                      rot={"base": 200000.0, "dims": 64}), 192),
     ],
 }
 
