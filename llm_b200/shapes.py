@@ -31,12 +31,37 @@ SHAPES = {
 }
 
 
-def shape(name: str, layers: int | None = None) -> dict:
-    """A copy of the named shape's config.json, optionally with fewer layers."""
+def _guberax(width, heads, kv_heads, dim, vdim, ff, vocab, layers, window):
+    """A Guberax configuration whose layers match a Llama shape in size: width, heads, feed-forward and
+    vocabulary alike, a key row of two maps as wide as a Llama key (2 * dim), values of vdim."""
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": 4, "diff": 0.3,
+             "scale": dim ** -0.5, "mask": {"size": window, "keep_first": 4},
+             "rot": {"base": 500000.0, "dims": dim,
+                     "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    return {"architecture": "Guberax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}}] * layers}
+
+
+# the layer sizes of llama-3.1-8b and llama-3.2-1b; the window is wider than the contexts they are
+# compared at unless a run narrows it
+SHAPES["guberax-8b"] = _guberax(4096, 32, 8, 64, 128, 14336, 128256, 32, 1 << 20)
+SHAPES["guberax-1b"] = _guberax(2048, 32, 8, 32, 64, 8192, 128256, 16, 1 << 20)
+
+
+def shape(name: str, layers: int | None = None, window: int | None = None) -> dict:
+    """A copy of the named shape's config.json, optionally with fewer layers (and, for a shape
+    with windowed attention, another window)."""
+    import copy
     from .errors import FormatError
     if name not in SHAPES:
         raise FormatError(f"unknown shape '{name}' (known: {', '.join(sorted(SHAPES))})")
-    raw = dict(SHAPES[name])
-    if layers is not None:
+    raw = copy.deepcopy(SHAPES[name])
+    if isinstance(raw.get("layers"), list):
+        if layers is not None:
+            raw["layers"] = [copy.deepcopy(raw["layers"][0]) for _ in range(layers)]
+        if window is not None:
+            for layer in raw["layers"]:
+                layer["mixer"]["mask"]["size"] = window
+    elif layers is not None:
         raw["num_hidden_layers"] = layers
     return raw
