@@ -214,9 +214,12 @@ __device__ __forceinline__ bool key_visible(int key, int pos, int window, int ke
 // a1 - lambda a2, the head's norm and the scale, and store.
 constexpr int PF_WARPS = 8;
 constexpr int BQ = 64;
+#ifndef LLMB_DIFF_PF_BLOCKS
+#define LLMB_DIFF_PF_BLOCKS 2              // blocks an SM the prefill kernel is compiled for (128 registers a thread)
+#endif
 
 template <int DK, int DV>
-__global__ void __launch_bounds__(PF_WARPS * 32)
+__global__ void __launch_bounds__(PF_WARPS * 32, LLMB_DIFF_PF_BLOCKS)
 diff_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                     int table_stride, int ring_pages, const int* __restrict__ cu_seqlens,

@@ -117,6 +117,98 @@ conv_rope_cache_kernel(ConvArgs a) {
     }
 }
 
+// The same work for bfloat16 with 16-byte accesses: a thread takes 8 neighbouring channels of a token.
+// Needs every width, unit and rotated part to be a multiple of 8, pairs (2i, 2i + 1) (a pair then lies
+// inside a thread's 8 channels) or no rotation, and 16-byte aligned rows. The thread that owns the
+// channels also shifts their state in a decode step.
+template <int TAPS>
+__global__ void __launch_bounds__(256)
+conv_rope_cache_vec_kernel(ConvArgs a) {
+    griddep_launch();
+    griddep_wait();
+    using bf16 = __nv_bfloat16;
+    int t = blockIdx.x;
+    int channels = a.q_width + a.k_width + a.v_width;
+    int pos = a.tok_pos[t], b = a.tok_seq[t];
+    int first_token = a.cu_seqlens[b];
+    int start = pos - (t - first_token);
+    bf16* state_row = a.state ? (bf16*)a.state + (size_t)a.slot_ids[b] * (TAPS - 1) * channels : nullptr;
+    int half = a.n_rot >> 1;
+    size_t page = 0;
+    int row = pos % LLMB_PAGE;
+    if (a.write_cache) page = a.block_table[(size_t)b * a.table_stride + ((pos / LLMB_PAGE) % a.ring_pages)];
+    const float* angles = a.table ? a.table + (size_t)pos * a.n_rot : nullptr;
+    const bf16* u = (const bf16*)a.u;
+    int k_end = a.q_width + a.k_width;
+
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8; c < channels; c += gridDim.y * blockDim.x * 8) {
+        uint4 taps_raw[TAPS];                            // the rows positions pos - TAPS + 1 .. pos, oldest first
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+            int p = pos - TAPS + 1 + j;
+            const bf16* src = p >= start ? u + (size_t)(first_token + (p - start)) * a.u_stride + c
+                                         : state_row + (size_t)((TAPS - 1) - (start - p)) * channels + c;
+            taps_raw[j] = *reinterpret_cast<const uint4*>(src);
+        }
+        float y[8];
+        if (a.w) {
+            float w[8 * TAPS];
+            const float4* wp = reinterpret_cast<const float4*>(a.w + (size_t)c * TAPS);
+#pragma unroll
+            for (int i = 0; i < 2 * TAPS; ++i) {
+                float4 v = wp[i];
+                w[4 * i] = v.x; w[4 * i + 1] = v.y; w[4 * i + 2] = v.z; w[4 * i + 3] = v.w;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                float sum = 0.f;
+#pragma unroll
+                for (int j = 0; j < TAPS; ++j)
+                    sum = fmaf(w[e * TAPS + j], __bfloat162float(reinterpret_cast<const bf16*>(&taps_raw[j])[e]), sum);
+                y[e] = sum;
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = __bfloat162float(reinterpret_cast<const bf16*>(&taps_raw[TAPS - 1])[e]);
+        }
+        bool is_q = c < a.q_width, is_k = !is_q && c < k_end;
+        if ((is_q || is_k) && angles) {
+            int d = (is_q ? c : c - a.q_width) % a.rot_unit;
+            if (d < a.n_rot) {
+                float4 cs = *reinterpret_cast<const float4*>(angles + (d >> 1));
+                float4 sn = *reinterpret_cast<const float4*>(angles + half + (d >> 1));
+                float cv[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float lo = y[2 * i], hi = y[2 * i + 1];
+                    y[2 * i] = lo * cv[i] - hi * sv[i];
+                    y[2 * i + 1] = hi * cv[i] + lo * sv[i];
+                }
+            }
+        }
+        uint4 packed;
+        __nv_bfloat162* out2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out2[i] = __floats2bfloat162_rn(y[2 * i], y[2 * i + 1]);
+        if (is_q) {
+            *reinterpret_cast<uint4*>((bf16*)a.q_out + (size_t)t * a.q_width + c) = packed;
+        } else if (a.write_cache) {
+            if (is_k) {
+                int local = c - a.q_width, head = local / a.k_dim, d = local - head * a.k_dim;
+                *reinterpret_cast<uint4*>((bf16*)a.k_cache + ((page * a.k_heads + head) * LLMB_PAGE + row) * a.k_dim + d) = packed;
+            } else {
+                int local = c - k_end, head = local / a.v_dim, d = local - head * a.v_dim;
+                *reinterpret_cast<uint4*>((bf16*)a.v_cache + ((page * a.v_heads + head) * LLMB_PAGE + row) * a.v_dim + d) = packed;
+            }
+        }
+        if (a.update_state && TAPS > 1 && a.w) {         // one token of this sequence: the rows move up by one
+#pragma unroll
+            for (int j = 1; j < TAPS; ++j)
+                *reinterpret_cast<uint4*>(state_row + (size_t)(j - 1) * channels + c) = taps_raw[j];
+        }
+    }
+}
+
 // The state after a step: the last taps - 1 rows of (old state rows, the step's rows). One block
 // column per sequence; a thread owns a channel, reads its rows and then writes them.
 template <typename T>
@@ -167,17 +259,40 @@ LLMB_EXPORT int llmb_conv_rope_cache_write(
     a.k_cache = k_cache; a.k_heads = k_heads; a.k_dim = k_dim; a.v_cache = v_cache; a.v_heads = v_heads; a.v_dim = v_dim;
     a.write_cache = write_cache;
     a.update_state = single_tokens ? 1 : 0;
-    // one block row per token; where a step has few tokens the channels are spread over block columns
-    // (not when the kernel shifts the state itself: a rotation partner may lie in another column)
+    // one block row per token; where a step has few tokens the channels are spread over block columns.
+    // A block takes chunks of 256 neighbouring channels, so a pair (2i, 2i + 1) of units of even size never
+    // leaves its block; a kernel that shifts the state itself AND rotates pairs that may lie in another
+    // chunk must keep a token in one block (the partner's state row would be read by one block and
+    // shifted by another).
     int columns = 1;
-    if (!a.update_state || !a.state) {
+    if (!a.update_state || !a.state || !a.table || (a.interleaved && a.rot_unit % 2 == 0)) {
         columns = ceil_div(channels, 256);
         while (columns > 1 && (long long)n_tokens * columns > 148 * 8) columns = (columns + 1) / 2;
     }
-    dim3 grid(n_tokens, columns);
-    if (dtype == LLMB_DTYPE_F32) llmb::launch(conv_rope_cache_kernel<float>, grid, 256, 0, stream, true, a);
-    else if (dtype == LLMB_DTYPE_BF16) llmb::launch(conv_rope_cache_kernel<__nv_bfloat16>, grid, 256, 0, stream, true, a);
-    else return fail(LLMB_ERR_ARGUMENT, "short_conv: unknown dtype %d", dtype);
+    // 16-byte path: bfloat16, everything a multiple of 8 channels and aligned, pairs inside a thread's channels
+    auto aligned16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    bool vector = dtype == LLMB_DTYPE_BF16 && q_width % 8 == 0 && k_width % 8 == 0 && v_width % 8 == 0 && u_stride % 8 == 0 &&
+                  aligned16(u) && aligned16(q_out) && aligned16(a.state) && aligned16(w) &&
+                  (!write_cache || (k_dim % 8 == 0 && v_dim % 8 == 0 && aligned16(k_cache) && aligned16(v_cache))) &&
+                  (a.table == nullptr || (interleaved && n_rot % 8 == 0 && a.rot_unit % 8 == 0 && aligned16(table)));
+    if (vector) {
+        int vectors = channels / 8;
+        int cols = ceil_div(vectors, 256);
+        while (cols > 1 && (long long)n_tokens * cols > 148 * 16) cols = (cols + 1) / 2;
+        dim3 vgrid(n_tokens, cols);
+        int threads = vectors < 256 ? ((vectors + 31) / 32) * 32 : 256;
+        switch (a.taps) {
+#define LLMB_CONV_CASE(N) case N: llmb::launch(conv_rope_cache_vec_kernel<N>, vgrid, threads, 0, stream, true, a); break;
+            LLMB_CONV_CASE(1) LLMB_CONV_CASE(2) LLMB_CONV_CASE(3) LLMB_CONV_CASE(4)
+            LLMB_CONV_CASE(5) LLMB_CONV_CASE(6) LLMB_CONV_CASE(7) LLMB_CONV_CASE(8)
+#undef LLMB_CONV_CASE
+        }
+    } else {
+        dim3 grid(n_tokens, columns);
+        if (dtype == LLMB_DTYPE_F32) llmb::launch(conv_rope_cache_kernel<float>, grid, 256, 0, stream, true, a);
+        else if (dtype == LLMB_DTYPE_BF16) llmb::launch(conv_rope_cache_kernel<__nv_bfloat16>, grid, 256, 0, stream, true, a);
+        else return fail(LLMB_ERR_ARGUMENT, "short_conv: unknown dtype %d", dtype);
+    }
     int code = check_launch("conv_rope_cache_write");
     if (code != LLMB_OK || a.state == nullptr || a.update_state) return code;
     dim3 state_grid(n_seqs, ceil_div(channels, 256) < 8 ? ceil_div(channels, 256) : 8);

@@ -79,7 +79,8 @@ def _close(got, want, dtype, what=""):
 @pytest.mark.parametrize("case", [
     # heads, kv heads, map size, value size, taps, rotated, interleaved
     (4, 2, 6, 10, 3, 4, True), (3, 3, 10, 7, 2, 10, True), (2, 1, 16, 24, 4, 8, False), (4, 1, 48, 96, 4, 48, True),
-    (2, 2, 8, 12, 0, 0, True), (2, 1, 16, 16, 1, 16, True), (1, 1, 5, 3, 8, 2, True)])
+    (2, 2, 8, 12, 0, 0, True), (2, 1, 16, 16, 1, 16, True), (1, 1, 5, 3, 8, 2, True),
+    (2, 2, 32, 64, 3, 16, True), (2, 2, 16, 24, 0, 0, True), (4, 2, 64, 128, 8, 64, True), (2, 1, 16, 32, 2, 0, True)])
 def test_conv_rope_cache_write(dtype, case):
     ops = _ops()
     heads, groups, dim, vdim, taps, n_rot, interleaved = case
