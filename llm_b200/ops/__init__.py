@@ -423,7 +423,7 @@ def rope_cache_write(qkv, rope_table, tok_pos, tok_seq, block_table, ring_pages,
 
 def conv_rope_cache_write(u, conv_w, state, tok_pos, tok_seq, cu_seqlens, seq_lens, slot_ids, rope_table,
                           rot_unit, interleaved, q_out, k_width, v_width, block_table, ring_pages, k_cache,
-                          v_cache, write_cache=True, single_tokens=False):
+                          v_cache, write_cache=True, single_tokens=False, conv_w_rows=None):
     """What lies between the q/k/v projection and the attention of a mixer with a short convolution:
     a causal convolution over time on every channel of `u` [T, Cq + Ck + Cv] (weights `conv_w`
     float32 [C, taps], or None for no convolution; `state` [slots, taps - 1, C] in u's dtype holds the
@@ -432,8 +432,9 @@ def conv_rope_cache_write(u, conv_w, state, tok_pos, tok_seq, cu_seqlens, seq_le
     rotation), queries to `q_out` [T, Cq], keys and values into the paged cache
     (k_cache [pages, Hk, 64, Dk], v_cache [pages, Hv, 64, Dv] with Hk * Dk = Ck, Hv * Dv = Cv).
     `single_tokens`: every sequence brings exactly one token (the kernel then shifts the state
-    itself; otherwise a second kernel does)."""
-    _require_cuda(u, conv_w, state, tok_pos, tok_seq, cu_seqlens, seq_lens, slot_ids, rope_table, q_out,
+    itself; otherwise a second kernel does). `conv_w_rows` (optional): the taps once more as
+    bfloat16 [taps, C], exact copies, for the 16-byte kernel of bfloat16 runs."""
+    _require_cuda(u, conv_w, conv_w_rows, state, tok_pos, tok_seq, cu_seqlens, seq_lens, slot_ids, rope_table, q_out,
                   block_table, k_cache, v_cache)
     n, q_width = q_out.shape
     channels = q_width + k_width + v_width
@@ -454,9 +455,12 @@ def conv_rope_cache_write(u, conv_w, state, tok_pos, tok_seq, cu_seqlens, seq_le
             raise KernelError("conv_rope_cache_write: the table of angles must be contiguous float32")
     if k_cache.dtype != u.dtype or v_cache.dtype != u.dtype or not k_cache.is_contiguous() or not v_cache.is_contiguous():
         raise KernelError("conv_rope_cache_write: the cache must be contiguous and of the projection's dtype")
+    if conv_w_rows is not None and (conv_w is None or conv_w_rows.dtype != torch.bfloat16
+                                    or tuple(conv_w_rows.shape) != (taps, channels) or not conv_w_rows.is_contiguous()):
+        raise KernelError(f"conv_rope_cache_write: the taps' copy must be contiguous bfloat16 [{taps}, {channels}]")
     kernels = 2 if (conv_w is not None and taps > 1 and not single_tokens) else 1
     _call("short_conv", "llmb_conv_rope_cache_write", _ptr(u), _c_int(u.stride(0)), _c_int(_code(u.dtype)),
-          _ptr(conv_w), _c_int(taps), _ptr(state), _ptr(tok_pos), _ptr(tok_seq), _ptr(cu_seqlens), _ptr(seq_lens),
+          _ptr(conv_w), _ptr(conv_w_rows), _c_int(taps), _ptr(state), _ptr(tok_pos), _ptr(tok_seq), _ptr(cu_seqlens), _ptr(seq_lens),
           _ptr(slot_ids), _ptr(rope_table), _c_int(n_rot), _c_int(rot_unit), _c_int(1 if interleaved else 0),
           _ptr(q_out), _c_int(q_width), _c_int(k_width), _c_int(v_width), _ptr(block_table),
           _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(k_cache), _c_int(k_cache.shape[1]),

@@ -41,7 +41,7 @@ class DiffAttentionMixer(Mixer):
             raise FormatError("a window, the kept first tokens and the taps of a convolution cannot be negative")
         self.spec = spec
         self.position = build_position(spec.position)
-        self.w_qkv = self.w_o = self.w_conv = None
+        self.w_qkv = self.w_o = self.w_conv = self.w_conv_rows = None
         self.lam = 0.0
 
     @property
@@ -79,12 +79,15 @@ class DiffAttentionMixer(Mixer):
         return out
 
     def bind(self, tensors, dtype, device):
-        import math
         t, s = self.spec.tensor, self.spec
         self.w_qkv = torch.cat([to_run_dtype(tensors[t[r]], dtype, device) for r in ("q", "k", "v")])
         self.w_o = to_run_dtype(tensors[t["o"]], dtype, device)
         if s.conv_taps:
             self.w_conv = torch.cat([to_float32(tensors[t[r + "_conv"]], device) for r in ("q", "k", "v")]).contiguous()
+            # bfloat16 runs: the taps once more as [taps, channels] in bfloat16 for the 16-byte kernel, where
+            # that loses nothing (taps stored as bfloat16)
+            rows = self.w_conv.t().contiguous().to(torch.bfloat16)
+            self.w_conv_rows = rows if dtype == torch.bfloat16 and torch.equal(rows.float().t(), self.w_conv) else None
         lq1, lk1, lq2, lk2 = (tensors[t[r]].to(torch.float32).cpu() for r in ("lq1", "lk1", "lq2", "lk2"))
         first = torch.exp((lq1 * lk1).sum())               # 32-bit, as the layer's other gates
         second = torch.exp((lq2 * lk2).sum())
@@ -156,7 +159,8 @@ class DiffAttentionMixer(Mixer):
             qkv, self.w_conv, state, ctx.tok_pos, ctx.tok_seq, ctx.cu_seqlens, ctx.seq_lens, ctx.slot_ids,
             self.position.table if self.position is not None else None, s.head_dim,
             self.position.interleaved if self.position is not None else False, queries, self.k_width,
-            self.v_width, table, ring, keys, values, write_cache=(entry == cache_entry), single_tokens=ctx.decode)
+            self.v_width, table, ring, keys, values, write_cache=(entry == cache_entry), single_tokens=ctx.decode,
+            conv_w_rows=self.w_conv_rows)
         mixed = ops.diff_attention(
             queries, keys, values, table, ring, ctx.tok_pos, ctx.tok_seq, s.n_heads, s.n_kv_heads, s.head_dim,
             s.value_dim, s.scale, s.window, s.keep_first, self.lam, s.eps, 1.0 - s.diff, head_norm=True,

@@ -158,7 +158,7 @@ def add_rows_(x, y, emit=None):
 
 def conv_rope_cache_write(u, conv_w, state, tok_pos, tok_seq, cu_seqlens, seq_lens, slot_ids, rope_table,
                           rot_unit, interleaved, q_out, k_width, v_width, block_table, ring_pages, k_cache,
-                          v_cache, write_cache=True, single_tokens=False):
+                          v_cache, write_cache=True, single_tokens=False, conv_w_rows=None):
     """Sequence by sequence: the rows before the step's first token come from the state, the
     convolution is a plain sum over taps, then every unit of `rot_unit` channels of q and k rotates."""
     n, q_width = q_out.shape

@@ -87,7 +87,10 @@ def test_conv_rope_cache_write(dtype, case):
     qw, kw, vw = heads * 2 * dim, groups * 2 * dim, groups * vdim
     channels = qw + kw + vw
     gen = torch.Generator().manual_seed(3)
-    for lengths, new in [([70, 5, 130, 64], [70, 2, 66, 1]), ([9, 200, 65], [1, 1, 1]), ([3], [3])]:
+    cases = [([70, 5, 130, 64], [70, 2, 66, 1]), ([9, 200, 65], [1, 1, 1]), ([3], [3])]
+    if dim % 8 == 0 and vdim % 8 == 0:                   # long steps: blocks walk several tokens, across sequence edges
+        cases.append(([1500, 7, 300, 77, 901], [1493, 7, 129, 1, 900]))
+    for lengths, new in cases:
         batch = Batch(lengths, new, seed=len(lengths))
         u = torch.randn((batch.n_tokens, channels), generator=gen).to(dtype).to(DEV)
         w = torch.randn((channels, taps), generator=gen).to(DEV) if taps else None
@@ -98,21 +101,27 @@ def test_conv_rope_cache_write(dtype, case):
                     state[int(batch.slots[b])] = 0
         table = None
         if n_rot:
-            angle = torch.arange(256, dtype=torch.float64)[:, None] * torch.rand(n_rot // 2, generator=gen, dtype=torch.float64)
+            angle = torch.arange(1600, dtype=torch.float64)[:, None] * torch.rand(n_rot // 2, generator=gen, dtype=torch.float64)
             table = torch.cat([angle.cos(), angle.sin()], dim=1).float().to(DEV)
         results = []
-        for fn in (ops.conv_rope_cache_write, plain_ops.conv_rope_cache_write):
+        rows = w.t().contiguous().to(torch.bfloat16) if (taps and dtype == torch.bfloat16) else None
+        if rows is not None:                                             # the kernel may read the taps from their bfloat16 copy
+            w = rows.float().t().contiguous()
+        for fn in (ops.conv_rope_cache_write, plain_ops.conv_rope_cache_write, ops.conv_rope_cache_write):
             k_cache, v_cache = batch.caches(groups, 2 * dim, vdim, dtype, seed=5)
             held = state.clone() if state is not None else None
             q_out = torch.zeros((batch.n_tokens, qw), dtype=dtype, device=DEV)
             fn(u, w, held, batch.tok_pos, batch.tok_seq, batch.cu, batch.seq_lens, batch.slots, table, dim,
                interleaved, q_out, kw, vw, batch.table, batch.width, k_cache, v_cache,
-               write_cache=True, single_tokens=all(k == 1 for k in new))
+               write_cache=True, single_tokens=all(k == 1 for k in new),
+               conv_w_rows=rows if len(results) == 2 else None)
             results.append((q_out, k_cache, v_cache, held))
         torch.cuda.synchronize()
         for got, want, what in zip(results[0], results[1], ("queries", "keys", "values", "state")):
             if got is not None:
                 _close(got, want, dtype, what)
+        for got, other in zip(results[0], results[2]):                   # with and without the taps' copy: the same bits
+            assert got is None or torch.equal(got, other)
         if state is not None:                                            # the state holds the last rows exactly
             assert torch.equal(results[0][3], results[1][3])
 
