@@ -146,60 +146,49 @@ conv_rope_cache_vec_kernel(ConvArgs a) {
         bool is_q = c < a.q_width, is_k = !is_q && c < k_end;
         int rot_place = (is_q || is_k) ? (is_q ? c : c - a.q_width) % a.rot_unit : 0;
         bool rotates = (is_q || is_k) && a.table != nullptr && rot_place < a.n_rot;
-        // the taps of this thread's channels, widened once
-        float wf[TAPS][8];
-        if (a.w_rows) {
-#pragma unroll
-            for (int j = 0; j < TAPS; ++j) {
-                uint4 w_raw = *reinterpret_cast<const uint4*>((const bf16*)a.w_rows + (size_t)j * channels + c);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) wf[j][e] = __bfloat162float(reinterpret_cast<const bf16*>(&w_raw)[e]);
-            }
-        } else if (a.w) {
-#pragma unroll
-            for (int j = 0; j < TAPS; ++j)
-#pragma unroll
-                for (int e = 0; e < 8; ++e) wf[j][e] = a.w[(size_t)(c + e) * TAPS + j];
-        }
-        // the newest row of a token is requested one token ahead: the stores of a token may alias the
-        // loads of the next for all the compiler knows, and would otherwise chain the tokens' latencies
-        int ahead_pos = a.tok_pos[t_begin], ahead_seq = a.tok_seq[t_begin];
-        uint4 ahead = *reinterpret_cast<const uint4*>(u + (size_t)t_begin * a.u_stride + c);
         for (int t = t_begin; t < t_end; ++t) {
-            int pos = ahead_pos, b = ahead_seq;
+            int pos = a.tok_pos[t], b = a.tok_seq[t];
             bf16* state_row = nullptr;
             if (b == prev_seq && pos == prev_pos + 1) {
 #pragma unroll
                 for (int j = 0; j + 1 < TAPS; ++j) taps_raw[j] = taps_raw[j + 1];
+                taps_raw[TAPS - 1] = *reinterpret_cast<const uint4*>(u + (size_t)t * a.u_stride + c);
             } else {
                 int first_token = a.cu_seqlens[b];
                 int start = pos - (t - first_token);
                 if (a.state) state_row = (bf16*)a.state + (size_t)a.slot_ids[b] * (TAPS - 1) * channels;
 #pragma unroll
-                for (int j = 0; j + 1 < TAPS; ++j) {
+                for (int j = 0; j < TAPS; ++j) {
                     int p = pos - TAPS + 1 + j;
                     const bf16* src = p >= start ? u + (size_t)(first_token + (p - start)) * a.u_stride + c
                                                  : state_row + (size_t)((TAPS - 1) - (start - p)) * channels + c;
                     taps_raw[j] = *reinterpret_cast<const uint4*>(src);
                 }
             }
-            taps_raw[TAPS - 1] = ahead;
-            if (t + 1 < t_end) {
-                ahead_pos = a.tok_pos[t + 1];
-                ahead_seq = a.tok_seq[t + 1];
-                ahead = *reinterpret_cast<const uint4*>(u + (size_t)(t + 1) * a.u_stride + c);
-            }
             prev_seq = b;
             prev_pos = pos;
             float y[8];
-            if (a.w) {
+            if (a.w_rows) {                              // one coalesced 16-byte load a tap
 #pragma unroll
                 for (int e = 0; e < 8; ++e) y[e] = 0.f;
 #pragma unroll
-                for (int j = 0; j < TAPS; ++j)
+                for (int j = 0; j < TAPS; ++j) {
+                    uint4 w_raw = *reinterpret_cast<const uint4*>((const bf16*)a.w_rows + (size_t)j * channels + c);
 #pragma unroll
                     for (int e = 0; e < 8; ++e)
-                        y[e] = fmaf(wf[j][e], __bfloat162float(reinterpret_cast<const bf16*>(&taps_raw[j])[e]), y[e]);
+                        y[e] = fmaf(__bfloat162float(reinterpret_cast<const bf16*>(&w_raw)[e]),
+                                    __bfloat162float(reinterpret_cast<const bf16*>(&taps_raw[j])[e]), y[e]);
+                }
+            } else if (a.w) {
+                const float* w = a.w + (size_t)c * TAPS;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float sum = 0.f;
+#pragma unroll
+                    for (int j = 0; j < TAPS; ++j)
+                        sum = fmaf(w[e * TAPS + j], __bfloat162float(reinterpret_cast<const bf16*>(&taps_raw[j])[e]), sum);
+                    y[e] = sum;
+                }
             } else {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) y[e] = __bfloat162float(reinterpret_cast<const bf16*>(&taps_raw[TAPS - 1])[e]);
@@ -315,8 +304,6 @@ LLMB_EXPORT int llmb_conv_rope_cache_write(
         // long steps: a block walks 8 tokens (a row is fetched once, not once a tap); short ones: a block a token
         a.n_tokens = n_tokens;
         a.tile = (!a.update_state && n_tokens >= 2048) ? 8 : 1;
-        if (const char* forced = std::getenv("LLMB_CONV_TILE"))          // for measurements: force the tile
-            if (!a.update_state && std::atoi(forced) > 0) a.tile = std::atoi(forced);
         int rows = ceil_div(n_tokens, a.tile);
         int cols = ceil_div(vectors, 256);
         while (cols > 1 && (long long)rows * cols > 148 * 16) cols = (cols + 1) / 2;
