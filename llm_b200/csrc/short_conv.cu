@@ -304,6 +304,8 @@ LLMB_EXPORT int llmb_conv_rope_cache_write(
         // long steps: a block walks 8 tokens (a row is fetched once, not once a tap); short ones: a block a token
         a.n_tokens = n_tokens;
         a.tile = (!a.update_state && n_tokens >= 2048) ? 8 : 1;
+        if (const char* forced = std::getenv("LLMB_CONV_TILE"))          // for measurements: force the tile
+            if (!a.update_state && std::atoi(forced) > 0) a.tile = std::atoi(forced);
         int rows = ceil_div(n_tokens, a.tile);
         int cols = ceil_div(vectors, 256);
         while (cols > 1 && (long long)rows * cols > 148 * 16) cols = (cols + 1) / 2;
