@@ -444,7 +444,14 @@ diff_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
 // values. Four warps take 16 keys of a page each; the warps, then the slices (a second kernel),
 // are merged in a fixed order, and the merge forms a1 - lambda a2, the head's norm and the scale.
 constexpr int DC_WARPS = 4;
-constexpr int DC_STAGES = 3;
+// Pages in a block's ring: as many as fit in about 110 KB (two blocks an SM), between 3 and 8; small
+// pages need more of them in flight to keep HBM busy.
+template <int DK, int DV>
+__host__ __device__ constexpr int decode_stages() {
+    constexpr int bytes = LLMB_PAGE * (2 * DK + PAD + DV + PAD) * 2;
+    constexpr int fit = (110 * 1024) / bytes;
+    return fit < 3 ? 3 : fit > 8 ? 8 : fit;
+}
 
 template <int DV>
 __device__ __forceinline__ void diff_finish(float* a1, const float* a2, float lambda, float eps, float out_scale,
@@ -473,6 +480,7 @@ diff_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          float eps, float out_scale, int head_norm) {
     constexpr int LDK = 2 * DK + PAD, LDV = DV + PAD;
     constexpr int K_ELEMS = LLMB_PAGE * LDK, STAGE_ELEMS = K_ELEMS + LLMB_PAGE * LDV;
+    constexpr int DC_STAGES = decode_stages<DK, DV>();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     griddep_launch();
@@ -718,7 +726,7 @@ static int launch_decode(const void* q, int q_stride, const void* k_cache, const
                          int out_stride, float* scratch, int n_seqs, int n_heads, int n_kv_heads, float scale, int window,
                          int keep_first, float lambda, float eps, float out_scale, int head_norm, int n_splits,
                          cudaStream_t stream) {
-    size_t stage_bytes = (size_t)DC_STAGES * LLMB_PAGE * (2 * DK + PAD + DV + PAD) * sizeof(__nv_bfloat16);
+    size_t stage_bytes = (size_t)decode_stages<DK, DV>() * LLMB_PAGE * (2 * DK + PAD + DV + PAD) * sizeof(__nv_bfloat16);
     size_t merge_bytes = (size_t)(DC_WARPS * 16 * DV + 2 * DC_WARPS * 16 + 16 * DV) * sizeof(float);
     size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
     static bool configured = false;
