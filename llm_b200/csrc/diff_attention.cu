@@ -444,8 +444,10 @@ diff_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __n
 // values. Four warps take 16 keys of a page each; the warps, then the slices (a second kernel),
 // are merged in a fixed order, and the merge forms a1 - lambda a2, the head's norm and the scale.
 constexpr int DC_WARPS = 4;
-// Pages in a block's ring: as many as fit in about 110 KB (two blocks an SM), between 3 and 8; small
-// pages need more of them in flight to keep HBM busy.
+// Pages in a block's ring. A launch of few blocks (up to two an SM) takes as many as fit in about 110 KB,
+// between 3 and 8: small pages need more of them in flight to keep HBM busy. A launch of many blocks takes
+// 3, so that more blocks share an SM (measured at maps of 32 and values of 64, context 8,192: batch 8
+// 945 -> 846 us a step with the deep ring, batch 64 2,108 -> 2,475 us).
 template <int DK, int DV>
 __host__ __device__ constexpr int decode_stages() {
     constexpr int bytes = LLMB_PAGE * (2 * DK + PAD + DV + PAD) * 2;
@@ -469,7 +471,7 @@ __device__ __forceinline__ void diff_finish(float* a1, const float* a2, float la
 }
 
 // partials: acc [seq, head, map, slice, DV], stats [seq, head, map, slice, 2] = (max in base-2 units, sum)
-template <int DK, int DV>
+template <int DK, int DV, int DC_STAGES>
 __global__ void __launch_bounds__(DC_WARPS * 32)
 diff_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                          const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
@@ -480,7 +482,6 @@ diff_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          float eps, float out_scale, int head_norm) {
     constexpr int LDK = 2 * DK + PAD, LDV = DV + PAD;
     constexpr int K_ELEMS = LLMB_PAGE * LDK, STAGE_ELEMS = K_ELEMS + LLMB_PAGE * LDV;
-    constexpr int DC_STAGES = decode_stages<DK, DV>();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);
     griddep_launch();
@@ -726,22 +727,31 @@ static int launch_decode(const void* q, int q_stride, const void* k_cache, const
                          int out_stride, float* scratch, int n_seqs, int n_heads, int n_kv_heads, float scale, int window,
                          int keep_first, float lambda, float eps, float out_scale, int head_norm, int n_splits,
                          cudaStream_t stream) {
-    size_t stage_bytes = (size_t)decode_stages<DK, DV>() * LLMB_PAGE * (2 * DK + PAD + DV + PAD) * sizeof(__nv_bfloat16);
+    constexpr int DEEP = decode_stages<DK, DV>();
+    bool deep = DEEP > 3 && (long long)n_splits * n_kv_heads * n_seqs <= 2 * 148;
+    int stages = deep ? DEEP : 3;
+    size_t stage_bytes = (size_t)stages * LLMB_PAGE * (2 * DK + PAD + DV + PAD) * sizeof(__nv_bfloat16);
     size_t merge_bytes = (size_t)(DC_WARPS * 16 * DV + 2 * DC_WARPS * 16 + 16 * DV) * sizeof(float);
     size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
     static bool configured = false;
     if (!configured) {
-        LLMB_CUDA(cudaFuncSetAttribute(diff_decode_split_kernel<DK, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        size_t most = (size_t)DEEP * LLMB_PAGE * (2 * DK + PAD + DV + PAD) * sizeof(__nv_bfloat16);
+        most = most > merge_bytes ? most : merge_bytes;
+        LLMB_CUDA(cudaFuncSetAttribute(diff_decode_split_kernel<DK, DV, DEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
+        LLMB_CUDA(cudaFuncSetAttribute(diff_decode_split_kernel<DK, DV, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most));
         configured = true;
     }
     float* part_acc = scratch;
     float* part_stats = scratch + (size_t)n_seqs * n_heads * 2 * n_splits * DV;
     dim3 grid(n_splits, n_kv_heads, n_seqs);
-    llmb::launch(diff_decode_split_kernel<DK, DV>, grid, DC_WARPS * 32, smem, stream, true,
-                 (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
-                 block_table, table_stride, ring_pages, seq_lens, seq_order, part_acc, part_stats, (__nv_bfloat16*)out,
-                 out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f, window, keep_first, lambda, eps, out_scale,
-                 head_norm);
+#define LLMB_DIFF_DECODE(STAGES)                                                                                       \
+    llmb::launch(diff_decode_split_kernel<DK, DV, STAGES>, grid, DC_WARPS * 32, smem, stream, true,                      \
+                 (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,      \
+                 block_table, table_stride, ring_pages, seq_lens, seq_order, part_acc, part_stats, (__nv_bfloat16*)out, \
+                 out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f, window, keep_first, lambda, eps,         \
+                 out_scale, head_norm)
+    if (deep) LLMB_DIFF_DECODE(DEEP); else LLMB_DIFF_DECODE(3);
+#undef LLMB_DIFF_DECODE
     int code = check_launch("diff_attention_decode_split");
     if (code || n_splits == 1) return code;
     llmb::launch(diff_decode_combine_kernel<DV>, dim3(n_heads, n_seqs), 64, 0, stream, true, (const float*)part_acc,

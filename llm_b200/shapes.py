@@ -34,11 +34,11 @@ SHAPES = {
 def _guberax(width, heads, kv_heads, dim, vdim, ff, vocab, layers, window):
     """A Guberax configuration whose layers match a Llama shape in size: width, heads, feed-forward and
     vocabulary alike, a key row of two maps as wide as a Llama key (2 * dim), values of vdim."""
-    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": 4, "diff": 0.3,
+    mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "conv": 4, "diff": 0.25,
              "scale": dim ** -0.5, "mask": {"size": window, "keep_first": 4},
              "rot": {"base": 500000.0, "dims": dim,
                      "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
-    return {"architecture": "Guberax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+    return {"architecture": "Guberax", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 50.0,
             "layers": [{"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}}] * layers}
 
 

@@ -150,7 +150,7 @@ def test_unequal_batch_slot_reuse_and_early_ends(tmp_path, plain_kernels):
     lengths = [1, 13, 30, 66]
     seqs = [random_tokens(n + 5, config["vocab"], 20 + i) for i, n in enumerate(lengths)]
     expected = [plain.forward(config, weights, s) for s in seqs]
-    for _ in range(2):                                   # the second round runs on slots and pages that were used
+    for _ in range(2):                                   # the second time runs on slots and pages that were used
         slots = engine.acquire(len(seqs))
         logits = engine.step([Entry(s, q[:n], [n - 1]) for s, q, n in zip(slots, seqs, lengths)])
         for b, n in enumerate(lengths):

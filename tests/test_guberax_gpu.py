@@ -78,7 +78,7 @@ def _close(got, want, dtype, what=""):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("case", [
     # heads, kv heads, map size, value size, taps, rotated, interleaved
-    (4, 2, 6, 10, 3, 4, True), (3, 3, 10, 7, 2, 10, True), (2, 1, 16, 24, 4, 8, False), (4, 1, 48, 96, 4, 48, True),
+    (4, 2, 6, 10, 3, 4, True), (3, 3, 10, 7, 2, 10, True), (2, 1, 16, 24, 4, 8, False), (4, 2, 48, 96, 3, 32, True),
     (2, 2, 8, 12, 0, 0, True), (2, 1, 16, 16, 1, 16, True), (1, 1, 5, 3, 8, 2, True),
     (2, 2, 32, 64, 3, 16, True), (2, 2, 16, 24, 0, 0, True), (4, 2, 64, 128, 8, 64, True), (2, 1, 16, 32, 2, 0, True)])
 def test_conv_rope_cache_write(dtype, case):
@@ -184,16 +184,23 @@ def test_diff_attention_prefill_kernel(shape, window, keep_first):
 @pytest.mark.parametrize("window,keep_first", [(0, 0), (70, 3), (64, 0), (33, 65), (200, 1)])
 def test_diff_attention_decode_kernel(shape, window, keep_first, monkeypatch):
     """The split-KV decode kernel at lengths on, before and behind page edges, with one and several slices
-    (also more slices than pages), groups of 1, 4 and 8 heads."""
+    (also more slices than pages), groups of 1, 3 and 8 heads."""
     dim, vdim = shape
     lengths = [1, 63, 64, 65, 128, 129, 300, 700]
-    for heads, groups in [(4, 4), (4, 1), (8, 1)]:
+    for heads, groups in [(4, 4), (6, 2), (8, 1)]:
         for splits in ("1", "2", "8"):
             monkeypatch.setenv("LLMB_DECODE_SPLITS", splits)
             batch = Batch(lengths, [1] * len(lengths), seed=window + dim)
             got, want = _attention_both(batch, heads, groups, dim, vdim, torch.bfloat16, window, keep_first, decode=True,
                                         variant="diff_attention_decode")
             _close(got, want, torch.bfloat16, (shape, window, keep_first, heads, splits))
+    # a launch of many blocks (the kernel then takes its short ring of pages)
+    monkeypatch.setenv("LLMB_DECODE_SPLITS", "2")
+    many = [1 + (37 * i) % 300 for i in range(40)]
+    batch = Batch(many, [1] * len(many), seed=dim)
+    got, want = _attention_both(batch, 4, 4, dim, vdim, torch.bfloat16, window, keep_first, decode=True,
+                                variant="diff_attention_decode")
+    _close(got, want, torch.bfloat16, (shape, window, keep_first, "many blocks"))
 
 
 @pytest.mark.parametrize("variant,dtype", [("diff_attention_generic", torch.float32),
@@ -304,7 +311,7 @@ def test_whole_decode_pieces_and_batches_agree_with_plain(tmp_path, which, dtype
     lengths = [150, 1, 67, 20]
     seqs = [random_tokens(n, config["vocab"], 30 + n) for n in lengths]
     expected = [plain.forward(config, weights, s) for s in seqs]
-    for round_ in range(2):                                      # the second round reuses slots and pages
+    for again in range(2):                                       # the second time reuses slots and pages
         slots = engine.acquire(len(seqs))
         heads = [max(1, n - 9 - 2 * i) for i, n in enumerate(lengths)]          # unequal prompts, cut into passes of 48
         logits = engine.step([Entry(s, q[:h], list(range(h))) for s, q, h in zip(slots, seqs, heads)])
