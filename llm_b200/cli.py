@@ -247,7 +247,7 @@ def inspect(folder) -> int:
     params = sum(int(torch.tensor(p.shape).prod()) for p in expected.values())
     print(f"{'parameters':28s}{params:,} in {len(expected)} tensors")
     kv, states = model.cache_requests()
-    per_token = sum(2 * r.n_kv_heads * r.head_dim * 2 for r in kv if r is not None)
+    per_token = sum(r.n_kv_heads * (r.head_dim + (r.value_dim or r.head_dim)) * 2 for r in kv if r is not None)
     print(f"{'cache per token (bfloat16)':28s}{per_token / 1024:.1f} KiB")
     try:
         files = open_checkpoint(folder)

@@ -194,3 +194,41 @@ def test_random_model_writer_round_trip(tmp_path, plain_kernels):
     (slot,) = engine.acquire()
     logits = engine.step([Entry(slot, tokens, [19])])
     assert torch.allclose(logits[0], plain.forward(raw, weights, tokens)[19], **TOL)
+
+
+# ----------------------------------------------------------------------------- kernel choice and command line
+
+def test_kernel_choice_for_the_differential_attention():
+    from llm_b200.ops import tactics
+    names = {r.name for r in tactics.rows("diff_attention")}
+    assert names == {"diff_attention_decode", "diff_attention_prefill", "diff_attention_generic"}
+    assert all(r.evidence for r in tactics.rows("diff_attention"))
+    bf16, f32 = torch.bfloat16, torch.float32
+    choose = tactics.choose_diff_attention
+    assert choose(True, bf16, 32, 8, 64, 128, 4096, 4, True, True) == "diff_attention_decode"
+    assert choose(False, bf16, 32, 8, 64, 128, 4096, 4, True, True) == "diff_attention_prefill"
+    assert choose(True, bf16, 32, 2, 64, 128, 0, 0, True, True) == "diff_attention_prefill"        # a group of 16 heads: no decode tile
+    assert choose(False, bf16, 4, 2, 40, 72, 0, 0, True, True) == "diff_attention_generic"         # sizes no tile takes
+    assert choose(True, f32, 32, 8, 64, 128, 0, 0, True, True) == "diff_attention_generic"         # the 32-bit path
+    text = tactics.explain("diff_attention", decode=False, dtype=bf16, n_heads=4, n_kv_heads=2, head_dim=40,
+                           value_dim=72, window=0, keep_first=0, packed=True, aligned=True)
+    assert "map size 40 with value size 72" in text
+    tactics.disable("diff_attention_prefill")
+    try:
+        assert choose(False, bf16, 32, 8, 64, 128, 4096, 4, True, True) == "diff_attention_generic"
+    finally:
+        tactics.enable("diff_attention_prefill")
+
+
+def test_inspect_and_random_commands(tmp_path, capsys):
+    import json
+    from llm_b200 import cli
+    folder = make_folder(tmp_path, "Q", torch.bfloat16)
+    assert cli.inspect(str(folder)) == 0
+    out = capsys.readouterr().out
+    assert "architecture  Guberax" in out and "diff_attention_prefill" in out and "runnable" in out
+    config_file = tmp_path / "config.json"
+    config_file.write_text(json.dumps(GUB_P))
+    assert cli.random_folder(["--config", str(config_file), "--out", str(tmp_path / "made"), "--seed", "3"]) == 0
+    raw, weights = plain.read_model_folder(tmp_path / "made")
+    assert raw["architecture"] == "Guberax" and set(weights) == set(tensor_shapes(GUB_P))

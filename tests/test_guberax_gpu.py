@@ -437,3 +437,14 @@ def test_trace_replay_program(tmp_path):
     _check_logits(read(0), wa[[0, 29]], torch.float32)
     _check_logits(read(1), torch.stack([wa[30], wb[8]]), torch.float32)
     _check_logits(read(2), wa[39:40], torch.float32)
+
+
+def test_a_group_no_decode_tile_holds():
+    """16 query heads on one key/value head: the decode kernel's tile has 8 rows a map, so a decode step runs on
+    the prefill kernel (one query a sequence); and with sizes no tile takes, on the generic kernel."""
+    lengths = [1, 64, 65, 200, 333]
+    batch = Batch(lengths, [1] * len(lengths), seed=5)
+    got, want = _attention_both(batch, 16, 1, 32, 64, torch.bfloat16, 70, 3, decode=True, variant=None)
+    _close(got, want, torch.bfloat16, "prefill kernel in a decode step")
+    got, want = _attention_both(batch, 16, 1, 24, 40, torch.bfloat16, 70, 3, decode=True, variant=None)
+    _close(got, want, torch.bfloat16, "generic kernel in a decode step")
