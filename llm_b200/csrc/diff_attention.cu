@@ -5,8 +5,8 @@
 //   o = a1 - lambda * a2,   o <- o / sqrt(mean(o^2) + eps) * out_scale      (over the head's vdim values)
 //
 // with lambda one number of the layer. Which keys a query at position p sees: j <= p and
-// (window == 0 or p - j < window or j < keep_first): a sliding window that also keeps the
-// sequence's first tokens, at their true positions. Keys [pages, G, 64, 2 * dim], values
+// (window == 0 or p - j < window or j < keep_first): a sliding window beside which the sequence's
+// first keep_first tokens stay visible, rotated and counted at the positions they have. Keys [pages, G, 64, 2 * dim], values
 // [pages, G, 64, vdim]; query head h reads key/value head h / (H / G).
 //
 // This file holds the kernel for any sizes in 32-bit arithmetic: the kernel of the true 32-bit

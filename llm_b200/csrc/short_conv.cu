@@ -2,7 +2,8 @@
 // it carries from step to step, fused with what follows it in an attention mixer: the rotation of
 // queries and keys and the write of keys and values into the paged cache.
 //
-//   y[t, c] = sum_j w[c, j] * u[pos(t) - taps + 1 + j, c]        (zeros before the sequence's start)
+//   y[t, c] = w[c, 0] u[p - (n - 1), c] + ... + w[c, n - 1] u[p, c],   n taps, p the position of token t,
+//   u = 0 at negative positions
 //
 // u is the projection of the step's tokens [T, C] (queries | keys | values side by side). Values
 // of positions before the step's first token come from the sequence's state [slots, taps - 1, C]:

@@ -11,18 +11,19 @@ from .base import Mixer, build_position, register_mixer, to_float32, to_run_dtyp
 
 
 class DiffAttentionMixer(Mixer):
-    """Every query head holds two maps. With q = W_q h laid out head by head as [map 1, map 2]
-    (H * 2 * dim rows), k likewise (G * 2 * dim rows) and v (G * vdim rows):
+    """Every query head holds two maps. The q projection gives, for each of the H heads in turn, the
+    query of map 1 and then the query of map 2 (dim elements each); the k projection the same for
+    the G key/value heads; the v projection one value of vdim elements per key/value head. Then:
 
-    * optionally a causal convolution over time on every channel of q, k and v
-      (y_t = sum_j w[:, j] u_(t - taps + 1 + j), zeros before the sequence), whose last
-      taps - 1 inputs are per-sequence state;
+    * optionally a causal convolution over time on every channel of q, k and v: with n taps,
+      y[t] = tap[0] u[t - (n - 1)] + ... + tap[n - 1] u[t], u = 0 at negative positions; the last
+      n - 1 inputs of a sequence are its state;
     * rotation of the first `rotary_dim` elements of every map of q and k;
     * per map a softmax attention over the keys a position sees (causal; with a window, the keys
       less than `window` back and the first `keep_first` of the sequence), both maps over the same
       values: a1, a2;
-    * o = a1 - lambda a2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff, then
-      o / sqrt(mean(o^2) + eps) over the head's values, times 1 - diff;
+    * o = a1 - lambda a2, lambda = e^<lq1, lk1> - e^<lq2, lk2> + diff; o is divided by the root of
+      (its mean square + eps) over the head's values and multiplied by 1 - diff;
     * the output projection, added to the residual stream.
 
     One launch for the projection, one for convolution + rotation + cache write

@@ -63,7 +63,7 @@ class AttentionSpec:
 class DiffAttentionSpec:
     """Differential attention: every query head has two maps, each a softmax attention of its own
     over the same values; a head's result is map 1 minus lambda times map 2, divided by its root
-    mean square and multiplied by 1 - diff. lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff."""
+    mean square and multiplied by 1 - diff. lambda = e^<lq1, lk1> - e^<lq2, lk2> + diff."""
     hidden: int
     n_heads: int
     n_kv_heads: int

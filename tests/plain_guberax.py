@@ -37,7 +37,7 @@ def read_model_folder(folder):
 # ----------------------------------------------------------------------------- mechanisms
 
 def offset_norm(x, weight, eps):
-    """x / sqrt(mean(x^2) + eps) * (1 + weight)."""
+    """x * (1 + weight) / r, r = the root of (the mean of x's squares + eps)."""
     return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps) * (1.0 + weight)
 
 
