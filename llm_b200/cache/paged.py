@@ -45,11 +45,12 @@ class KvRequest:
     head_dim: int
     window: int = 0            # 0: keep every position
     value_dim: int | None = None   # width of a value, where it differs from a key's (None: head_dim)
+    values_are_keys: bool = False  # the mixer's values are its cached keys: one tensor, no second one
 
     @property
     def group_key(self):
         return ("window" if self.window else "full", self.n_kv_heads, self.head_dim, self.window,
-                self.value_dim or self.head_dim)
+                0 if self.values_are_keys else (self.value_dim or self.head_dim))
 
 
 @dataclass(frozen=True)
@@ -88,7 +89,7 @@ class Group:
     n_kv_heads: int
     head_dim: int
     window: int
-    value_dim: int = 0                                # width of a value (== head_dim unless a mixer asks otherwise)
+    value_dim: int = 0                                # width of a value (== head_dim unless a mixer asks otherwise; 0: the keys are the values)
     entries: list = field(default_factory=list)     # schedule positions that own storage here
     ring_pages: int = 0                               # logical pages per sequence
     pool: FreeList | None = None
@@ -123,8 +124,7 @@ class PagedCache:
             key = request.group_key
             if key not in by_key:
                 by_key[key] = len(self.groups)
-                self.groups.append(Group(key[0], request.n_kv_heads, request.head_dim, request.window,
-                                         request.value_dim or request.head_dim))
+                self.groups.append(Group(key[0], request.n_kv_heads, request.head_dim, request.window, key[4]))
             g = by_key[key]
             self.entry_group.append((g, len(self.groups[g].entries)))
             self.groups[g].entries.append(entry)
@@ -143,7 +143,11 @@ class PagedCache:
             group.pool = FreeList(n_pages.value, f"page of the {group.kind} group",
                                   _borrowed=lib.llmh_cache_list(handle, g), _owner=self)
             group.slot_pages = _SlotPages(self, g)
-            if group.value_dim == group.head_dim:
+            if group.value_dim == 0:                          # values are the keys: one tensor serves as both
+                group.keys = torch.zeros((len(group.entries), n_pages.value, group.n_kv_heads, PAGE, group.head_dim),
+                                         dtype=dtype, device=self.device)
+                group.values = group.keys
+            elif group.value_dim == group.head_dim:
                 group.storage = torch.zeros(
                     (len(group.entries), 2, n_pages.value, group.n_kv_heads, PAGE, group.head_dim),
                     dtype=dtype, device=self.device)
@@ -240,7 +244,7 @@ class PagedCache:
 
     def bytes(self) -> int:
         total = sum(t.numel() * t.element_size() for g in self.groups
-                    for t in (g.storage, g.keys, g.values) if t is not None)
+                    for t in (g.storage, g.keys, g.values if g.values is not g.keys else None) if t is not None)
         total += sum(s.numel() * s.element_size() for s in self.states if s is not None)
         return total
 

@@ -1,11 +1,13 @@
 from .base import ConfigReader, read_config_json
 from .guberax import GuberaxConfig
 from .llama import LlamaConfig
+from .mefolorn import MefolornConfig
 from .registry import (config_class_for, config_from_dict, known_architectures, load_config,
                        register_architecture)
 
 register_architecture(LlamaConfig.architecture, LlamaConfig)
 register_architecture(GuberaxConfig.architecture, GuberaxConfig)
+register_architecture(MefolornConfig.architecture, MefolornConfig)
 
-__all__ = ["ConfigReader", "read_config_json", "LlamaConfig", "GuberaxConfig", "config_class_for",
+__all__ = ["ConfigReader", "read_config_json", "LlamaConfig", "GuberaxConfig", "MefolornConfig", "config_class_for",
            "config_from_dict", "known_architectures", "load_config", "register_architecture"]

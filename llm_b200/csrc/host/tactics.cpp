@@ -125,6 +125,14 @@ std::string diff_prefill_guard(const Shape& s) {
     return diff_tc_guard(s);
 }
 
+std::string sigmoid_generic_guard(const Shape& s) {
+    if (s.head_dim > LLMB_MAX_HEAD_DIM || s.value_dim > LLMB_MAX_HEAD_DIM)
+        return "head size " + std::to_string(s.head_dim) + " or value size " + std::to_string(s.value_dim) + " exceeds " +
+               std::to_string(LLMB_MAX_HEAD_DIM);
+    if (s.n_heads > 128) return std::to_string(s.n_heads) + " heads exceed 128";
+    return "";
+}
+
 const std::vector<Row>& table(int family) {
     static const std::vector<Row> linear = {
         {"gemm_tc", 30, tc_guard,
@@ -170,7 +178,13 @@ const std::vector<Row>& table(int family) {
          "one block per (token, head), both maps in one pass over the visible keys, 32-bit arithmetic, any sizes "
          "up to 256, any group, window and kept first tokens; the only variant of the 32-bit path"},
     };
-    return family == 0 ? linear : family == 1 ? attention : diff_attention;
+    static const std::vector<Row> sigmoid_attention = {
+        {"sigmoid_attention_generic", 0, sigmoid_generic_guard,
+         "one block per (token, head): the scores of all heads for a key, mixed over the heads, sigmoid weights, "
+         "32-bit arithmetic, any sizes up to 256, up to 128 heads, any group and window; the only variant of the "
+         "32-bit path"},
+    };
+    return family == 0 ? linear : family == 1 ? attention : family == 2 ? diff_attention : sigmoid_attention;
 }
 
 std::set<std::string>& switched_off() {
@@ -200,18 +214,18 @@ void copy_out(const std::string& text, char* out, int capacity) {
 
 }  // namespace
 
-// family: 0 products, 1 attention, 2 differential attention. shape: 12 ints {m, n, k, lda, decode, n_heads,
-// n_kv_heads, head_dim, window, packed, bf16, aligned}, for family 2 two more {value_dim, keep_first}. name and
+// family: 0 products, 1 attention, 2 differential attention, 3 sigmoid attention. shape: 12 ints {m, n, k, lda, decode,
+// n_heads, n_kv_heads, head_dim, window, packed, bf16, aligned}, for families 2 and 3 two more {value_dim, keep_first}. name and
 // reasons are filled up to their capacities.
 LLMH_EXPORT int llmh_tactics_choose(int family, const int* shape, char* name, int name_capacity, char* reasons,
                                     int reasons_capacity) {
     return guarded([&] {
-        if (family < 0 || family > 2) throw Failure{LLMH_FORMAT, "unknown kernel family"};
+        if (family < 0 || family > 3) throw Failure{LLMH_FORMAT, "unknown kernel family"};
         Shape s;
         s.m = shape[0]; s.n = shape[1]; s.k = shape[2]; s.lda = shape[3];
         s.decode = shape[4]; s.n_heads = std::max(shape[5], 1); s.n_kv_heads = std::max(shape[6], 1);
         s.head_dim = shape[7]; s.window = shape[8]; s.packed = shape[9]; s.bf16 = shape[10]; s.aligned = shape[11];
-        if (family == 2) { s.value_dim = shape[12]; s.keep_first = shape[13]; }
+        if (family >= 2) { s.value_dim = shape[12]; s.keep_first = shape[13]; }
         std::string why;
         copy_out(choose(family, s, &why), name, name_capacity);
         copy_out(why, reasons, reasons_capacity);
@@ -226,10 +240,10 @@ LLMH_EXPORT void llmh_tactics_set_disabled(const char* name, int disabled) {
 }
 LLMH_EXPORT int llmh_tactics_is_disabled(const char* name) { return switched_off().count(name) ? 1 : 0; }
 
-LLMH_EXPORT int llmh_tactics_rows(int family) { return (family >= 0 && family <= 2) ? (int)table(family).size() : 0; }
+LLMH_EXPORT int llmh_tactics_rows(int family) { return (family >= 0 && family <= 3) ? (int)table(family).size() : 0; }
 LLMH_EXPORT int llmh_tactics_row(int family, int index, const char** name, int* rank, const char** evidence) {
     return guarded([&] {
-        if (family < 0 || family > 2 || index < 0 || index >= (int)table(family).size())
+        if (family < 0 || family > 3 || index < 0 || index >= (int)table(family).size())
             throw Failure{LLMH_INVARIANT, "no such row"};
         const Row& row = table(family)[index];
         *name = row.name;

@@ -383,6 +383,69 @@ def rmsnorm(x, gain, eps, out_dtype, rows=None, out=None):
     return out
 
 
+def tanh_norm(x, alpha: float, gain, bias, out_dtype, rows=None, out=None):
+    """out[r, :] = tanh(alpha * x[rows[r] or r, :]) * gain + bias; x, gain and bias float32."""
+    _require_cuda(x, gain, bias, rows)
+    hidden = x.shape[-1]
+    n = rows.numel() if rows is not None else x.shape[0]
+    if (x.dtype != torch.float32 or gain.dtype != torch.float32 or bias.dtype != torch.float32
+            or not x.is_contiguous() or gain.numel() != hidden or bias.numel() != hidden):
+        raise KernelError("tanh_norm: x, gain and bias must be float32, x contiguous, gain and bias of x's width")
+    _check_out(out, (n, hidden), out_dtype, "tanh_norm")
+    if out is None:
+        out = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+    _call("elementwise", "llmb_tanh_norm", _ptr(x), _ptr(gain), _ptr(bias), _c_float(alpha), _ptr(rows), _ptr(out),
+          _c_int(_code(out_dtype)), _c_int(n), _c_int(hidden), _stream())
+    return out
+
+
+def _check_rows(t, n: int, width: int, dtype, what: str):
+    """A [n, width] tensor of `dtype` whose rows are contiguous (it may be a range of columns of a wider one)."""
+    _require_cuda(t)
+    if t.dim() != 2 or tuple(t.shape) != (n, width) or t.dtype != dtype or (width > 1 and t.stride(1) != 1):
+        raise KernelError(f"{what}: {tuple(t.shape)} {t.dtype} is not [{n}, {width}] {dtype} with contiguous rows")
+
+
+def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rope_table, rot_unit, interleaved,
+                          tok_pos, tok_seq, q_out, block_table, ring_pages, k_cache, v_cache, write_cache=True):
+    """What lies between a projection and the attention of a mixer that norms whole projections:
+    the first q_width columns of `u` are the queries, the next k_width the keys, the next v_width
+    the values (u may have more columns). With `q_gain` (float32 [q_width]) the queries of a token
+    are divided by the root of (the mean of all their squares + eps) and multiplied by the gain;
+    `k_gain` does the same for the keys. Then every unit of `rot_unit` columns of both is rotated
+    by `rope_table` [positions, n_rot] (None: no rotation). Queries go to `q_out` [T, q_width],
+    keys into k_cache [pages, Hk, 64, Dk] (Hk * Dk = k_width), values (v_width > 0) into v_cache
+    [pages, Hv, 64, Dv]. Sums, the norm's factor and angles are 32-bit."""
+    _require_cuda(u, q_gain, k_gain, rope_table, tok_pos, tok_seq, q_out, block_table, k_cache, v_cache)
+    n = q_out.shape[0]
+    if u.dim() != 2 or u.shape[0] != n or u.shape[1] < q_width + k_width + v_width or u.stride(1) != 1:
+        raise KernelError(f"norm_rope_cache_write: u {tuple(u.shape)} does not hold [{n}, {q_width} + {k_width} + {v_width}]")
+    _check_rows(q_out, n, q_width, u.dtype, "norm_rope_cache_write: q_out")
+    for gain, width in ((q_gain, q_width), (k_gain, k_width)):
+        if gain is not None and (gain.dtype != torch.float32 or gain.numel() != width or not gain.is_contiguous()):
+            raise KernelError(f"norm_rope_cache_write: a gain must be contiguous float32 [{width}]")
+    n_rot = 0
+    if rope_table is not None:
+        n_rot = rope_table.shape[1]
+        if (rope_table.dtype != torch.float32 or not rope_table.is_contiguous() or n_rot % 2 or n_rot > rot_unit
+                or q_width % rot_unit or k_width % rot_unit):
+            raise KernelError("norm_rope_cache_write: the table of angles must be contiguous float32 [positions, n_rot] "
+                              f"with an even n_rot <= {rot_unit}, and the units must divide both widths")
+    if (k_cache.dtype != u.dtype or not k_cache.is_contiguous() or k_cache.shape[1] * k_cache.shape[3] != k_width
+            or k_cache.shape[2] != PAGE):
+        raise KernelError(f"norm_rope_cache_write: the key cache {tuple(k_cache.shape)} does not fit keys of {k_width}")
+    if v_width and (v_cache is None or v_cache.dtype != u.dtype or not v_cache.is_contiguous()
+                    or v_cache.shape[1] * v_cache.shape[3] != v_width or v_cache.shape[2] != PAGE):
+        raise KernelError(f"norm_rope_cache_write: the value cache does not fit values of {v_width}")
+    _call("projection_norm", "llmb_norm_rope_cache_write", _ptr(u), _c_int(u.stride(0)), _c_int(_code(u.dtype)),
+          _c_int(q_width), _c_int(k_width), _c_int(v_width), _ptr(q_gain), _ptr(k_gain), _c_float(eps),
+          _ptr(rope_table), _c_int(n_rot), _c_int(rot_unit), _c_int(1 if interleaved else 0), _ptr(tok_pos),
+          _ptr(tok_seq), _ptr(q_out), _c_int(q_out.stride(0)), _ptr(block_table), _c_int(block_table.shape[1]),
+          _c_int(ring_pages), _ptr(k_cache), _ptr(v_cache if v_width else None), _c_int(1 if write_cache else 0),
+          _c_int(n), _stream())
+    return q_out
+
+
 def swiglu(gate_up, out=None):
     """act[t, f] = silu(gate_up[t, f]) * gate_up[t, F + f]."""
     _require_cuda(gate_up)
@@ -731,20 +794,37 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
 
 def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads,
               n_kv_heads, head_dim, scale, window=0, out=None, decode=False, seq_lens=None,
-              max_len=0, cu_seqlens=None, max_new=0, seq_order=None):
+              max_len=0, cu_seqlens=None, max_new=0, seq_order=None, sinks=None, gate=None, out_scale=1.0):
     """Causal grouped-query attention of the new tokens' queries (the first
     Hq * D columns of `qkv`) over the paged cache, which already holds the new
     tokens' keys and values. Returns [T, Hq * D] in qkv's dtype. `seq_order`
     (optional, int32 [B]): the sequences by falling length; the kernels that
-    take one block of work per sequence then start the longest first."""
-    _require_cuda(qkv, k_cache, v_cache, block_table, tok_pos, tok_seq)
+    take one block of work per sequence then start the longest first.
+
+    `sinks` (float32 [Hq]): e^sinks[a] is one more term of head a's softmax denominator; it has
+    no key and no value and is not scaled. `gate` ([T, Hq] in qkv's dtype, rows contiguous): the
+    result of head a for token t is multiplied by sigmoid(gate[t, a]). `out_scale` multiplies the
+    result. With any of the three, `out` may be a range of columns of a wider buffer. The value
+    cache may be the key cache itself (a mixer whose values are its keys)."""
+    _require_cuda(qkv, k_cache, v_cache, block_table, tok_pos, tok_seq, sinks, gate)
     n = qkv.shape[0]
-    _check_out(out, (n, n_heads * head_dim), qkv.dtype, "attention")
+    extras = sinks is not None or gate is not None or out_scale != 1.0
+    if extras:
+        if out is not None:
+            _check_rows(out, n, n_heads * head_dim, qkv.dtype, "attention: out")
+        if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != n_heads or not sinks.is_contiguous()):
+            raise KernelError(f"attention: sinks must be contiguous float32 [{n_heads}]")
+        if gate is not None:
+            _check_rows(gate, n, n_heads, qkv.dtype, "attention: gate")
+    else:
+        _check_out(out, (n, n_heads * head_dim), qkv.dtype, "attention")
     if out is None:
         out = torch.empty((n, n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
     variant = tactics.choose_attention(decode, qkv.dtype, n_heads, n_kv_heads, head_dim, window,
                                        cu_seqlens is not None and seq_lens is not None,
                                        qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0)
+    if extras and variant not in _ATTENTION_WITH_EXTRAS:
+        variant = "attention_generic"
     if variant == "attention_prefill_tc":
         _call("attention_prefill_tc", "llmb_attention_prefill_tc", _ptr(qkv), _c_int(qkv.stride(0)),
               _c_int(n), _ptr(k_cache), _ptr(v_cache), _c_int(k_cache.shape[0]), _ptr(block_table),
@@ -784,9 +864,94 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
               _c_int(ring_pages), _ptr(tok_pos), _ptr(tok_seq), _ptr(out), _c_int(out.stride(0)),
               _c_int(_code(qkv.dtype)), _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
-              _c_int(head_dim), _c_float(scale), _c_int(window), _stream())
+              _c_int(head_dim), _c_float(scale), _c_int(window), _ptr(sinks), _ptr(gate),
+              _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _stream())
     else:
         raise KernelError(f"attention: no kernel named {variant}")
+    return out
+
+
+# the attention kernels that take a sink, a gate and a scale of the result
+_ATTENTION_WITH_EXTRAS = ("attention_generic",)
+
+
+def attention_replay_key(step, n_kv_heads: int):
+    """What the launches of `attention` depend on beyond the token and sequence counts
+    (Part.replay_key): the most new tokens of a sequence (prefill grids), the slices (decode)."""
+    if step.decode:
+        return (True, decode_splits(step.n_seqs, n_kv_heads, step.max_len))
+    return (False, max(step.new_counts))
+
+
+def sigmoid_attention_replay_key(step, spec):
+    return (bool(step.decode), max(step.new_counts))
+
+
+def sigmoid_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads, n_kv_heads, dim, vdim,
+                      scale, window, talk, head_bias, out_scale, out, decode=False, seq_lens=None, max_len=0,
+                      cu_seqlens=None, max_new=0, seq_order=None):
+    """Causal grouped-query attention without a softmax, of the new tokens' queries q [T, H * dim]
+    over the paged cache (keys [pages, G, 64, dim], values [pages, G, 64, vdim]), which already
+    holds the new tokens. For query t at position p and every key j with j <= p (and p - j <
+    window, where window > 0): s_a = scale q_a . k_g(a),j; with `talk` (float32 [H, H])
+    s_a <- sum_b talk[a, b] s_b; with `head_bias` (float32 [H]) s_a += head_bias[a]; then
+    out[t, a] = out_scale * sum_j sigmoid(s_a) v_g(a),j. Scores, weights and sums are 32-bit.
+    `out` [T, H * vdim] in q's dtype may be a range of columns of a wider buffer."""
+    _require_cuda(q, k_cache, v_cache, block_table, tok_pos, tok_seq, talk, head_bias, out)
+    n = q.shape[0]
+    _check_rows(q, n, n_heads * dim, q.dtype, "sigmoid_attention: q")
+    _check_rows(out, n, n_heads * vdim, q.dtype, "sigmoid_attention: out")
+    if tuple(k_cache.shape[1:]) != (n_kv_heads, PAGE, dim) or tuple(v_cache.shape[1:]) != (n_kv_heads, PAGE, vdim):
+        raise KernelError(f"sigmoid_attention: the cache {tuple(k_cache.shape)} / {tuple(v_cache.shape)} does not fit "
+                          f"{n_kv_heads} heads of {dim} and {vdim}")
+    if talk is not None and (talk.dtype != torch.float32 or tuple(talk.shape) != (n_heads, n_heads) or not talk.is_contiguous()):
+        raise KernelError(f"sigmoid_attention: talk must be contiguous float32 [{n_heads}, {n_heads}]")
+    if head_bias is not None and (head_bias.dtype != torch.float32 or head_bias.numel() != n_heads):
+        raise KernelError(f"sigmoid_attention: head_bias must be float32 [{n_heads}]")
+    _call("sigmoid_attention", "llmb_sigmoid_attention_generic", _ptr(q), _c_int(q.stride(0)), _ptr(k_cache),
+          _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(tok_pos),
+          _ptr(tok_seq), _ptr(out), _c_int(out.stride(0)), _c_int(_code(q.dtype)), _c_int(n), _c_int(n_heads),
+          _c_int(n_kv_heads), _c_int(dim), _c_int(vdim), _c_float(scale), _c_int(window), _ptr(talk), _ptr(head_bias),
+          _c_float(out_scale), _stream())
+    return out
+
+
+def gated_recurrence(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_bias, rate, state, tok_seq,
+                     cu_seqlens, slot_ids, out, out_scale, work):
+    """A real-gated linear recurrence behind a short causal convolution, on C channels. `y`, `x`
+    [T, C] (the run's dtype; rows contiguous, may be column ranges): the two branches' projections
+    with their biases. u = conv_b + sum_j conv_w[:, j] * x[t - (taps - 1) + j] over the tokens of
+    a sequence (conv_w float32 [C, taps]; the inputs before the step's first token come from the
+    state). The channels are cut into gate_a.shape[0] equal parts; in part b,
+    r = sigmoid(gate_a[b] u_b + gate_a_bias), i = sigmoid(gate_i[b] u_b + gate_i_bias) (float32
+    [blocks, C / blocks, C / blocks], rows = outputs). a = exp(rate * r) (rate float32 [C], negative),
+    S <- a S + sqrt(1 - a^2) i u, out[t] = out_scale * S * gelu(y[t]) (tanh form). `state` float32
+    [slots, taps, C]: rows 0 .. taps - 2 the convolution's last inputs (oldest first), the last row
+    S; it is read at the slot of each sequence and brought up to date. `work` float32 [2, T, C]:
+    a and the driving term of every token, between the two kernels. Everything but the rounding of
+    `out` is 32-bit."""
+    _require_cuda(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_bias, rate, state, tok_seq, cu_seqlens,
+                  slot_ids, out, work)
+    n, channels = y.shape
+    taps, blocks = conv_w.shape[1], gate_a.shape[0]
+    _check_rows(y, n, channels, y.dtype, "gated_recurrence: y")
+    _check_rows(x, n, channels, y.dtype, "gated_recurrence: x")
+    _check_rows(out, n, channels, y.dtype, "gated_recurrence: out")
+    part = channels // max(blocks, 1)
+    for t, shape in ((conv_w, (channels, taps)), (conv_b, (channels,)), (gate_a, (blocks, part, part)),
+                     (gate_i, (blocks, part, part)), (gate_a_bias, (channels,)), (gate_i_bias, (channels,)),
+                     (rate, (channels,))):
+        if t.dtype != torch.float32 or tuple(t.shape) != shape or not t.is_contiguous():
+            raise KernelError(f"gated_recurrence: a parameter is {tuple(t.shape)} {t.dtype}, not contiguous float32 {shape}")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (taps, channels) or not state.is_contiguous():
+        raise KernelError(f"gated_recurrence: the state must be contiguous float32 [slots, {taps}, {channels}]")
+    if work.dtype != torch.float32 or tuple(work.shape) != (2, n, channels) or not work.is_contiguous():
+        raise KernelError(f"gated_recurrence: work must be contiguous float32 [2, {n}, {channels}]")
+    _call("gated_recurrence", "llmb_gated_recurrence", _ptr(y), _c_int(y.stride(0)), _ptr(x), _c_int(x.stride(0)),
+          _c_int(_code(y.dtype)), _ptr(conv_w), _ptr(conv_b), _c_int(taps), _ptr(gate_a), _ptr(gate_a_bias),
+          _ptr(gate_i), _ptr(gate_i_bias), _c_int(blocks), _ptr(rate), _ptr(state), _ptr(tok_seq), _ptr(cu_seqlens),
+          _ptr(slot_ids), _ptr(out), _c_int(out.stride(0)), _c_float(out_scale), _ptr(work), _c_int(n),
+          _c_int(channels), _c_int(cu_seqlens.numel() - 1), _stream(), kernels=2)
     return out
 
 
@@ -903,6 +1068,7 @@ def required_libraries() -> list:
 
 
 __all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "random_normal_", "begin_recording", "end_recording", "RecordedPass", "scratch_generation", "Emit", "FoldedNorm", "RopeWrite", "cast_sumsq", "SUMSQ_LD", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
-           "softcap_", "add_rows_", "conv_rope_cache_write", "diff_attention",
+           "softcap_", "add_rows_", "conv_rope_cache_write", "diff_attention", "tanh_norm", "norm_rope_cache_write",
+           "sigmoid_attention", "gated_recurrence", "attention_replay_key", "sigmoid_attention_replay_key",
            "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "check_device_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

@@ -21,7 +21,7 @@ import torch
 
 from .. import native
 
-_FAMILY = {"linear": 0, "attention": 1, "diff_attention": 2}
+_FAMILY = {"linear": 0, "attention": 1, "diff_attention": 2, "sigmoid_attention": 3}
 
 
 @dataclass(frozen=True)
@@ -112,6 +112,17 @@ def choose_diff_attention(decode, dtype, n_heads, n_kv_heads, head_dim, value_di
         name = _chosen[key] = _choose("diff_attention", decode=decode, dtype=dtype, n_heads=n_heads,
                                       n_kv_heads=n_kv_heads, head_dim=head_dim, value_dim=value_dim, window=window,
                                       keep_first=keep_first, packed=packed, aligned=aligned)[0]
+    return name
+
+
+def choose_sigmoid_attention(decode, dtype, n_heads, n_kv_heads, head_dim, value_dim, window, packed=False,
+                             aligned=True) -> str:
+    key = ("sigmoid_attention", decode, dtype, n_heads, n_kv_heads, head_dim, value_dim, window, packed, aligned)
+    name = _chosen.get(key)
+    if name is None:
+        name = _chosen[key] = _choose("sigmoid_attention", decode=decode, dtype=dtype, n_heads=n_heads,
+                                      n_kv_heads=n_kv_heads, head_dim=head_dim, value_dim=value_dim, window=window,
+                                      packed=packed, aligned=aligned)[0]
     return name
 
 

@@ -7,11 +7,17 @@ from .attention import AttentionMixer
 from .block import ParallelBlock, PreNormBlock
 from .diff_attention import DiffAttentionMixer
 from .feedforward import GatedMlp
-from .norm import RmsNorm
+from .gated_recurrence import GatedRecurrenceMixer
+from .latent_attention import LatentAttentionMixer
+from .norm import RmsNorm, TanhNorm
+from .projected import ProjectedMixer
+from .side_by_side import SideBySideMixer
+from .sigmoid_attention import SigmoidAttentionMixer
 from .position import Rope, inverse_frequencies
 
 __all__ = ["spec", "Block", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding",
            "StepContext", "build_block", "build_feed_forward", "build_mixer", "build_norm",
            "build_position", "register_block", "register_feed_forward", "register_mixer",
            "register_norm", "register_position", "AttentionMixer", "DiffAttentionMixer", "ParallelBlock", "PreNormBlock", "GatedMlp",
-           "RmsNorm", "Rope", "inverse_frequencies"]
+           "RmsNorm", "Rope", "inverse_frequencies", "TanhNorm", "ProjectedMixer", "LatentAttentionMixer",
+           "SigmoidAttentionMixer", "GatedRecurrenceMixer", "SideBySideMixer"]

@@ -174,7 +174,8 @@ register_block("pre_norm", PreNormBlock)
 
 class ParallelBlock(Block):
     """x += mixer(norm(x)) + feed_forward(norm(x)): one norm whose output both parts read; both
-    add into the 32-bit residual stream. The feed-forward may be absent.
+    add into the 32-bit residual stream. The feed-forward may be absent, or read a second norm of
+    the same x (`ffn_norm` of the spec).
 
     In bfloat16 runs the norm is folded into both parts where both offer it (each multiplies the
     gain into its own first matrix; both products read the same bfloat16 rows and sums of squares
@@ -188,11 +189,14 @@ class ParallelBlock(Block):
         self.norm = build_norm(spec.norm)
         self.mixer = build_mixer(spec.mixer)
         self.feed_forward = build_feed_forward(spec.feed_forward) if spec.feed_forward is not None else None
+        # a feed-forward with a norm of its own (of the same x): both norms are kernels of their own
+        second = getattr(spec, "ffn_norm", None)
+        self.ffn_norm = build_norm(second) if second is not None and self.feed_forward is not None else None
         self.folded = False
 
     @property
     def parts(self):
-        return tuple(p for p in (self.norm, self.mixer, self.feed_forward) if p is not None)
+        return tuple(p for p in (self.norm, self.mixer, self.ffn_norm, self.feed_forward) if p is not None)
 
     @property
     def graph_safe(self):
@@ -213,7 +217,7 @@ class ParallelBlock(Block):
             p.bind(tensors, dtype, device)
         # all readers of the norm fold it, or none does (a part's weights change when it folds)
         self.folded = False
-        if FOLD_NORMS and dtype == torch.bfloat16 and getattr(self.norm, "foldable", False):
+        if FOLD_NORMS and dtype == torch.bfloat16 and getattr(self.norm, "foldable", False) and self.ffn_norm is None:
             readers = [p for p in (self.mixer, self.feed_forward) if p is not None]
             if all(type(p).fold_input_norm is not Part.fold_input_norm for p in readers) \
                     and self.norm.spec.size % 8 == 0:
@@ -266,6 +270,8 @@ class ParallelBlock(Block):
                    BufferRequest("s_block", sums, torch.float32, 0, ffn_end + 1)]
         else:
             out = [BufferRequest("h_block", (n_tokens, hidden), dtype, 0, ffn_end)]
+        if self.ffn_norm is not None:
+            out.append(BufferRequest("h_ffn", (n_tokens, hidden), dtype, 0, ffn_end))
         out += [r.shifted(1, "mixer.") for r in mixer]
         out += [r.shifted(ffn_start, "ffn.") for r in ffn]
         return out
@@ -284,6 +290,9 @@ class ParallelBlock(Block):
             h = ops.FoldedNorm(normed.rows, normed.sumsq, normed.parts, self.spec.norm.eps, self.spec.norm.size)
         else:
             h = self.norm.forward(x, ctx.dtype, out=ctx.scratch("h_block", tuple(x.shape), ctx.dtype))
+        # the feed-forward's own norm reads the same x as the mixer's: before the mixer adds into it
+        h_ffn = h if self.ffn_norm is None else self.ffn_norm.forward(
+            x, ctx.dtype, out=ctx.scratch("h_ffn", tuple(x.shape), ctx.dtype))
         last = self.feed_forward if self.feed_forward is not None else self.mixer
         prefixed("mixer.")
         if last is self.mixer and emit_next is not None and self.mixer.emits:
@@ -293,9 +302,9 @@ class ParallelBlock(Block):
         if self.feed_forward is not None:
             prefixed("ffn.")
             if emit_next is not None and self.feed_forward.emits:
-                self.feed_forward.forward(h, ctx, x, emit=emit_next)
+                self.feed_forward.forward(h_ffn, ctx, x, emit=emit_next)
             else:
-                self.feed_forward.forward(h, ctx, x)
+                self.feed_forward.forward(h_ffn, ctx, x)
         prefixed("")
         if emit_next is not None and not last.emits:
             ops.cast_sumsq(x, emit_next)

@@ -1,5 +1,7 @@
-"""RMSNorm."""
+"""Norms: RMSNorm, and the element-wise tanh norm."""
 from __future__ import annotations
+
+import torch
 
 from .. import ops
 from ..weights.loader import ParamSpec
@@ -36,3 +38,39 @@ class RmsNorm(Norm):
 
 
 register_norm("rmsnorm", RmsNorm)
+
+
+class TanhNorm(Norm):
+    """y = tanh(alpha x) * weight + bias with one learned number alpha (Zhu et al., "Transformers
+    without Normalization"): no mean and no variance of the row enters, so nothing of it can be
+    folded into a product behind it. alpha, weight and bias are held in 32-bit."""
+    graph_safe = True
+    libraries = ("elementwise",)
+    foldable = False
+
+    def __init__(self, spec):
+        self.spec = spec
+        self.alpha = 0.0
+        self.gain = self.bias = None
+
+    def parameters(self):
+        s = self.spec
+        return {s.weight: ParamSpec((s.size,), "gain"), s.bias: ParamSpec((s.size,), "bias"),
+                s.alpha: ParamSpec((), "gate_scalar")}
+
+    def bind(self, tensors, dtype, device):
+        self.gain = to_float32(tensors[self.spec.weight], device)
+        self.bias = to_float32(tensors[self.spec.bias], device)
+        self.alpha = float(tensors[self.spec.alpha].to(torch.float32).reshape(()).cpu())
+
+    def weights(self):
+        return [self.gain, self.bias]
+
+    def replay_key(self, step):
+        return ()
+
+    def forward(self, x, out_dtype, rows=None, out=None):
+        return ops.tanh_norm(x, self.alpha, self.gain, self.bias, out_dtype, rows, out=out)
+
+
+register_norm("tanh_norm", TanhNorm)

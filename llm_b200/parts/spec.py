@@ -26,6 +26,16 @@ class NormSpec:
 
 
 @dataclass(frozen=True)
+class TanhNormSpec:
+    """A norm without a statistic: y = tanh(alpha x) * weight + bias, element by element (alpha one number)."""
+    size: int
+    weight: str                      # tensor names
+    bias: str
+    alpha: str
+    kind: str = "tanh_norm"
+
+
+@dataclass(frozen=True)
 class PositionSpec:
     """Rotary encoding: angle = position * inv_freq[pair]."""
     head_dim: int
@@ -85,6 +95,90 @@ class DiffAttentionSpec:
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values of every head are made from one normed latent row per
+    position, and whose queries pass through a normed latent of their own: c_q = norm(W_dq h),
+    q = W_uq c_q, c = norm(W_dkv h), k = W_uk c, v = W_uv c. Only c is cached. Softmax over the
+    visible keys with, optionally, one learned term per head in the denominator (`sink`), and,
+    optionally, a sigmoid gate per head read from the mixer's input (`gate`)."""
+    hidden: int
+    n_heads: int
+    head_dim: int                    # query / key size of a head
+    value_dim: int
+    q_rank: int                      # size of the queries' latent
+    kv_rank: int                     # size of the cached latent
+    scale: float                     # multiplies q.k
+    window: int                      # 0: every earlier key; w > 0: keys less than w positions back
+    eps: float                       # of both latent norms
+    sink: bool
+    gate: bool
+    names: tuple                     # sorted (role, tensor name): dq, dq_norm, uq, dkv, dkv_norm, uk, uv, o (+ sink, gate)
+    out_scale: float = 1.0           # multiplies the mixer's result
+    kind: str = "latent_attention"
+
+    @property
+    def tensor(self):
+        return dict(self.names)
+
+
+@dataclass(frozen=True)
+class SigmoidAttentionSpec:
+    """Grouped-query attention without a softmax: the weight of a visible key is
+    sigmoid(score + bias[head]), not normalised over the keys. Before that, optionally, the heads'
+    scores of one (query, key) pair are mixed by a matrix (`talk`: score_h <- sum_g T[h, g] score_g).
+    With `qk_norm`, queries and keys are RMS-normed over their whole projection (all heads at
+    once) before the rotation."""
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    window: int
+    qk_norm: bool
+    eps: float                       # of the query / key norm
+    talk: bool
+    head_bias: bool
+    position: Optional[PositionSpec]
+    names: tuple                     # sorted (role, tensor name): q, k, v, o (+ q_norm, k_norm, talk, head_bias)
+    out_scale: float = 1.0
+    kind: str = "sigmoid_attention"
+
+    @property
+    def tensor(self):
+        return dict(self.names)
+
+
+@dataclass(frozen=True)
+class GatedRecurrenceSpec:
+    """A recurrent block with a real-gated linear recurrent unit (De et al., "Griffin"): two
+    branches of `width` channels, y = gelu(W_y h + b_y) and u = conv(W_x h + b_x) (causal, per
+    channel, `conv_taps` taps with a bias); the channels are cut into `blocks` equal parts, each
+    with its own square matrices for the recurrence gate r and the input gate i;
+    a = exp(-decay * r * softplus(lam)), S_t = a S_(t-1) + sqrt(1 - a^2) i u; result W_o (S * y)."""
+    hidden: int
+    width: int
+    blocks: int
+    conv_taps: int
+    decay: float                     # 8 in the published block
+    names: tuple                     # sorted (role, tensor name): y, y_bias, x, x_bias, conv, conv_bias, ra, ra_bias, ri, ri_bias, lam, o
+    out_scale: float = 1.0
+    kind: str = "gated_recurrence"
+
+    @property
+    def tensor(self):
+        return dict(self.names)
+
+
+@dataclass(frozen=True)
+class SideBySideSpec:
+    """Two mixers that read the same input; their results (each times its own `out_scale`) are added."""
+    left: object
+    right: object
+    kind: str = "side_by_side"
+
+
+@dataclass(frozen=True)
 class GatedMlpSpec:
     hidden: int
     intermediate: int
@@ -110,11 +204,13 @@ class BlockSpec:
 @dataclass(frozen=True)
 class ParallelBlockSpec:
     """x += mixer(norm(x)) + feed_forward(norm(x)): one norm, both parts read its output.
-    `feed_forward` may be None (a layer that only mixes)."""
+    `feed_forward` may be None (a layer that only mixes). With `ffn_norm` the feed-forward reads a
+    norm of its own, of the same x: x += mixer(norm(x)) + feed_forward(ffn_norm(x))."""
     norm: object
     mixer: object
     feed_forward: object
     kind: str = "parallel"
+    ffn_norm: object = None
 
 
 @dataclass(frozen=True)

@@ -14,7 +14,8 @@ class ParamSpec:
     """What a part expects under one tensor name.
 
     role: 'matrix' (an operand of a matrix product, held in the run dtype),
-    'gain' (a norm's weight; 'gain_offset' where it is stored as an offset from 1), 'bias', 'vector'
+    'gain' (a norm's weight; 'gain_offset' where it is stored as an offset from 1), 'bias', 'vector',
+    'gate_scalar' (one learned number, shape ())
     and 'taps' (small 32-bit operands: a gate's vector, a short convolution's taps), 'table'
     (integers, held as int32).
     Gains and biases are held in 32-bit whatever the file stores.

@@ -58,6 +58,8 @@ def random_tensors(expected: dict, seed: int, dtype=torch.bfloat16, std: float =
             normal_(tensor, tensor_key(seed, name), 1.0, gain_noise)
         elif spec.role == "gain_offset":                     # a norm's weight that is stored around zero
             normal_(tensor, tensor_key(seed, name), 0.0, gain_noise)
+        elif spec.role == "gate_scalar":                     # one learned number of the order of one half
+            normal_(tensor, tensor_key(seed, name), 0.5, gain_noise)
         elif spec.role == "taps":                            # a short convolution: taps of the order of 1 / taps
             normal_(tensor, tensor_key(seed, name), 0.0, 1.0 / max(spec.shape[-1], 1))
         else:

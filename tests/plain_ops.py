@@ -124,7 +124,9 @@ def rope_cache_write(qkv, rope_table, tok_pos, tok_seq, block_table, ring_pages,
 
 def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads,
               n_kv_heads, head_dim, scale, window=0, out=None, decode=False, seq_lens=None,
-              max_len=0, cu_seqlens=None, max_new=0, seq_order=None):
+              max_len=0, cu_seqlens=None, max_new=0, seq_order=None, sinks=None, gate=None, out_scale=1.0):
+    """`sinks` (float32 [heads]): e^sink is one more term of a head's softmax denominator. `gate`
+    ([T, heads]): head a of token t is multiplied by sigmoid(gate[t, a]). `out_scale` multiplies all."""
     n = qkv.shape[0]
     result = torch.zeros((n, n_heads * head_dim), dtype=torch.float32, device=qkv.device)
     group = n_heads // n_kv_heads
@@ -139,9 +141,120 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
         q = qkv[t, :n_heads * head_dim].to(torch.float32).view(n_heads, head_dim)
         for h in range(n_heads):
             scores = (keys[:, h // group, :] @ q[h]) * scale
-            p = torch.softmax(scores, dim=0)
-            result[t, h * head_dim:(h + 1) * head_dim] = p @ vals[:, h // group, :]
+            if sinks is None:
+                p = torch.softmax(scores, dim=0)
+            else:
+                top = torch.maximum(scores.max(), sinks[h].to(torch.float32))
+                e = torch.exp(scores - top)
+                p = e / (e.sum() + torch.exp(sinks[h] - top))
+            o = (p @ vals[:, h // group, :]) * out_scale
+            if gate is not None:
+                o = o * torch.sigmoid(gate[t, h].to(torch.float32))
+            result[t, h * head_dim:(h + 1) * head_dim] = o
+    if out is not None:
+        out.copy_(result.to(out.dtype))
+        return out
     return result.to(qkv.dtype)
+
+
+def tanh_norm(x, alpha, gain, bias, out_dtype, rows=None, out=None):
+    if rows is not None:
+        x = x[rows.long()]
+    y = (torch.tanh(x.to(torch.float32) * alpha) * gain + bias).to(out_dtype)
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y
+
+
+def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rope_table, rot_unit, interleaved,
+                          tok_pos, tok_seq, q_out, block_table, ring_pages, k_cache, v_cache, write_cache=True):
+    """The first q_width columns of u are the queries, the next k_width the keys, the next v_width
+    the values. With a gain, queries (keys) are divided by the root mean square of the whole
+    segment and multiplied by the gain; then every unit of rot_unit columns of both rotates."""
+    n = u.shape[0]
+    if n == 0:
+        return q_out
+    pos = tok_pos.long()
+
+    def segment(first, width, gain):
+        x = u[:, first:first + width].to(torch.float32)
+        if gain is not None:
+            x = x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps) * gain
+        if rope_table is not None:
+            half = rope_table.shape[1] // 2
+            x = _rotate(x.reshape(n, -1, rot_unit), rope_table[pos, :half], rope_table[pos, half:], interleaved)
+        return x.reshape(n, width)
+
+    q_out.copy_(segment(0, q_width, q_gain).to(q_out.dtype))
+    if write_cache:
+        pages = block_table.long()[tok_seq.long(), (pos // PAGE) % ring_pages]
+        rows = pos % PAGE
+        k = segment(q_width, k_width, k_gain)
+        k_cache[pages, :, rows, :] = k.reshape(n, k_cache.shape[1], k_cache.shape[3]).to(k_cache.dtype)
+        if v_width:
+            v = u[:, q_width + k_width:q_width + k_width + v_width]
+            v_cache[pages, :, rows, :] = v.reshape(n, v_cache.shape[1], v_cache.shape[3]).to(v_cache.dtype)
+    return q_out
+
+
+def sigmoid_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads, n_kv_heads, dim, vdim,
+                      scale, window, talk, head_bias, out_scale, out, decode=False, seq_lens=None, max_len=0,
+                      cu_seqlens=None, max_new=0, seq_order=None):
+    n = q.shape[0]
+    group = n_heads // n_kv_heads
+    table = block_table.long()
+    result = torch.zeros((n, n_heads * vdim), dtype=torch.float32, device=q.device)
+    for t in range(n):
+        pos, b = int(tok_pos[t]), int(tok_seq[t])
+        first = max(0, pos - window + 1) if window > 0 else 0
+        js = torch.arange(first, pos + 1, device=q.device)
+        pages = table[b, (js // PAGE) % ring_pages]
+        keys = k_cache[pages, :, js % PAGE, :].to(torch.float32)        # [n_keys, G, dim]
+        vals = v_cache[pages, :, js % PAGE, :].to(torch.float32)        # [n_keys, G, vdim]
+        heads = q[t].to(torch.float32).view(n_heads, dim)
+        scores = torch.stack([keys[:, a // group, :] @ heads[a] for a in range(n_heads)]) * scale    # [H, n_keys]
+        if talk is not None:
+            scores = talk.to(torch.float32) @ scores
+        if head_bias is not None:
+            scores = scores + head_bias.to(torch.float32)[:, None]
+        weights = torch.sigmoid(scores)
+        for a in range(n_heads):
+            result[t, a * vdim:(a + 1) * vdim] = (weights[a] @ vals[:, a // group, :]) * out_scale
+    out.copy_(result.to(out.dtype))
+    return out
+
+
+def gated_recurrence(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_bias, rate, state, tok_seq,
+                     cu_seqlens, slot_ids, out, out_scale, work):
+    """Sequence by sequence and token by token. state [slots, taps, C] float32: rows 0 .. taps - 2
+    are the convolution's last inputs (oldest first), the last row is S."""
+    n, channels = y.shape
+    if n == 0:
+        return out
+    taps, blocks = conv_w.shape[1], gate_a.shape[0]
+    cu = cu_seqlens.tolist()
+    result = torch.zeros((n, channels), dtype=torch.float32, device=y.device)
+    for b in range(len(cu) - 1):
+        slot = int(slot_ids[b])
+        history = state[slot, :taps - 1].clone()
+        s = state[slot, taps - 1].clone()
+        for t in range(cu[b], cu[b + 1]):
+            rows = torch.cat([history, x[t].to(torch.float32)[None]])                     # [taps, C]
+            u = conv_b + (conv_w.T * rows).sum(dim=0)
+            history = rows[1:]
+            parts = u.view(blocks, -1)
+            r = torch.sigmoid(torch.einsum("boi,bi->bo", gate_a, parts).reshape(-1) + gate_a_bias)
+            i = torch.sigmoid(torch.einsum("boi,bi->bo", gate_i, parts).reshape(-1) + gate_i_bias)
+            a = torch.exp(rate * r)
+            s = a * s + torch.sqrt(1.0 - a * a) * i * u
+            z = y[t].to(torch.float32)
+            gelu = 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z * z * z)))
+            result[t] = s * gelu * out_scale
+        state[slot, :taps - 1] = history
+        state[slot, taps - 1] = s
+    out.copy_(result.to(out.dtype))
+    return out
 
 
 def softcap_(x, cap):
@@ -347,7 +460,8 @@ def sample_rows(logits, params, iparams, recent, recent_len, rng_state, out, sta
 OPS = {"embed": embed, "scale_": scale_, "cast_sumsq": cast_sumsq, "rmsnorm": rmsnorm, "swiglu": swiglu, "linear": linear,
        "rope_cache_write": rope_cache_write, "attention": attention, "argmax_rows": argmax_rows,
        "softcap_": softcap_, "add_rows_": add_rows_, "conv_rope_cache_write": conv_rope_cache_write,
-       "diff_attention": diff_attention,
+       "diff_attention": diff_attention, "tanh_norm": tanh_norm, "norm_rope_cache_write": norm_rope_cache_write,
+       "sigmoid_attention": sigmoid_attention, "gated_recurrence": gated_recurrence,
        "sample_rows": sample_rows}
 
 
