@@ -22,20 +22,28 @@ using namespace llmb;
 
 LLMB_DEFINE_LAST_ERROR(llmb_attention_generic)
 
-constexpr int MAX_PER_LANE = LLMB_MAX_HEAD_DIM / 32;   // elements of a head per lane
+constexpr int GENERIC_MAX_HEAD_DIM = 512;              // head sizes above LLMB_MAX_HEAD_DIM run the wider instantiation
 constexpr int WARPS = 4;
 
 // AHEAD: keys a warp fetches together. Four hide the loads' latency where a step has few blocks
 // (decoding); with thousands of blocks the SMs are full of other blocks' work and the registers
 // of one key at a time keep more of them resident.
-template <typename T, int AHEAD>
+//
+// Three optional extras, all applied in 32-bit when the four partial results are merged: `sinks` [heads]
+// (e^sink is one more term of the head's softmax denominator: it has no key and no value and is not
+// scaled), `gate` [T, heads] (the head's result is multiplied by sigmoid(gate)), `out_scale`. When the
+// value cache IS the key cache (a mixer whose cached rows serve as both), a row is loaded once.
+template <typename T, int AHEAD, int MAX_PER_LANE>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__ k_cache,
                          const T* __restrict__ v_cache, const int* __restrict__ block_table,
                          int table_stride, int ring_pages, const int* __restrict__ tok_pos,
                          const int* __restrict__ tok_seq, T* __restrict__ out, int out_stride,
-                         int n_heads, int n_kv_heads, int head_dim, float scale, int window) {
+                         int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                         const float* __restrict__ sinks, const T* __restrict__ gate, int gate_stride,
+                         float out_scale) {
     int t = blockIdx.x, head = blockIdx.y;
+    const bool values_are_keys = k_cache == v_cache;
     int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     int kv_head = head / (n_heads / n_kv_heads);
     int pos = tok_pos[t];
@@ -68,7 +76,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
                 int d = lane + 32 * i;
                 bool live = visible && d < head_dim;
                 kv[u][i] = live ? to_float(k_cache[offset + d]) : 0.f;
-                vv[u][i] = live ? to_float(v_cache[offset + d]) : 0.f;
+                vv[u][i] = values_are_keys ? kv[u][i] : (live ? to_float(v_cache[offset + d]) : 0.f);
             }
         }
 #pragma unroll
@@ -104,12 +112,16 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
         float m = part_max[0];
 #pragma unroll
         for (int w = 1; w < WARPS; ++w) m = fmaxf(m, part_max[w]);
-        float weight[WARPS], denom = 0.f;
+        float sink = sinks ? sinks[head] : -INFINITY;
+        m = fmaxf(m, sink);
+        float weight[WARPS], denom = sinks ? expf(sink - m) : 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
             weight[w] = part_max[w] == -INFINITY ? 0.f : expf(part_max[w] - m);
             denom += part_sum[w] * weight[w];
         }
+        float factor = out_scale;
+        if (gate) factor *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)t * gate_stride + head])));
         T* o = out + (size_t)t * out_stride + (size_t)head * head_dim;
 #pragma unroll
         for (int i = 0; i < MAX_PER_LANE; ++i) {
@@ -118,7 +130,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
                 float v = 0.f;
 #pragma unroll
                 for (int w = 0; w < WARPS; ++w) v += part_acc[w][d] * weight[w];
-                o[d] = from_float<T>(v / denom);
+                o[d] = from_float<T>(factor == 1.0f ? v / denom : v / denom * factor);
             }
         }
     }
@@ -129,19 +141,27 @@ LLMB_EXPORT int llmb_attention_generic(const void* q, int q_stride, const void* 
                                        int table_stride, int ring_pages, const int* tok_pos,
                                        const int* tok_seq, void* out, int out_stride, int dtype,
                                        int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                       float scale, int window, cudaStream_t stream) {
+                                       float scale, int window, const float* sinks, const void* gate,
+                                       int gate_stride, float out_scale, cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
-    LLMB_REQUIRE(head_dim > 0 && head_dim <= 32 * MAX_PER_LANE,
-                 "attention_generic: head_dim %d exceeds %d", head_dim, 32 * MAX_PER_LANE);
+    LLMB_REQUIRE(head_dim > 0 && head_dim <= GENERIC_MAX_HEAD_DIM,
+                 "attention_generic: head_dim %d exceeds %d", head_dim, GENERIC_MAX_HEAD_DIM);
     LLMB_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0,
                  "attention_generic: %d heads are no multiple of %d kv heads", n_heads, n_kv_heads);
     LLMB_REQUIRE(n_heads <= 65535 && ring_pages > 0 && window >= 0, "attention_generic: bad sizes");
     dim3 grid(n_tokens, n_heads);
     bool few = (long long)n_tokens * n_heads < 4096;       // the result is the same either way
-#define LLMB_GENERIC(T, AHEAD)                                                                          \
-    attention_generic_kernel<T, AHEAD><<<grid, WARPS * 32, 0, stream>>>(                                 \
+    bool wide = head_dim > LLMB_MAX_HEAD_DIM;              // twice the registers a lane: only where the head needs them
+#define LLMB_GENERIC_AS(T, AHEAD, PER)                                                                  \
+    attention_generic_kernel<T, AHEAD, PER><<<grid, WARPS * 32, 0, stream>>>(                            \
         (const T*)q, q_stride, (const T*)k_cache, (const T*)v_cache, block_table, table_stride,         \
-        ring_pages, tok_pos, tok_seq, (T*)out, out_stride, n_heads, n_kv_heads, head_dim, scale, window)
+        ring_pages, tok_pos, tok_seq, (T*)out, out_stride, n_heads, n_kv_heads, head_dim, scale, window, \
+        sinks, (const T*)gate, gate_stride, out_scale)
+#define LLMB_GENERIC(T, AHEAD)                                                                          \
+    do {                                                                                                \
+        if (wide) LLMB_GENERIC_AS(T, 1, GENERIC_MAX_HEAD_DIM / 32);                                      \
+        else LLMB_GENERIC_AS(T, AHEAD, LLMB_MAX_HEAD_DIM / 32);                                          \
+    } while (0)
     if (dtype == LLMB_DTYPE_F32) {
         if (few) LLMB_GENERIC(float, 4); else LLMB_GENERIC(float, 1);
     } else if (dtype == LLMB_DTYPE_BF16) {
@@ -150,6 +170,7 @@ LLMB_EXPORT int llmb_attention_generic(const void* q, int q_stride, const void* 
         return fail(LLMB_ERR_ARGUMENT, "attention_generic: unknown dtype %d", dtype);
     }
 #undef LLMB_GENERIC
+#undef LLMB_GENERIC_AS
     return check_launch("attention_generic");
 }
 

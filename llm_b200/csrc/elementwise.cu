@@ -196,6 +196,64 @@ LLMB_EXPORT int llmb_rmsnorm(const float* x, const float* gain, const int* rows,
     return check_launch("rmsnorm");
 }
 
+// ----------------------------------------------------------------------------- the tanh norm
+// out[r, e] = tanh(alpha * x[rows[r] or r, e]) * gain[e] + bias[e]: a norm without a statistic, so every
+// element is its own. With a second set of parameters (gain2 != nullptr) the same rows of x are read once for
+// two norms (a layer whose mixer and feed-forward each have a norm of the same stream). tanhf keeps its
+// precise form (no fast-math flag is set).
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+tanh_norm_kernel(const float* __restrict__ x, const int* __restrict__ rows, int hidden, int vector,
+                 float alpha, const float* __restrict__ gain, const float* __restrict__ bias, TOut* __restrict__ out,
+                 float alpha2, const float* __restrict__ gain2, const float* __restrict__ bias2, TOut* __restrict__ out2) {
+    griddep_launch();
+    griddep_wait();
+    int r = blockIdx.x;
+    const float* in = x + (size_t)(rows ? rows[r] : r) * hidden;
+    TOut* o = out + (size_t)r * hidden;
+    TOut* o2 = gain2 ? out2 + (size_t)r * hidden : nullptr;
+    if (vector) {
+        for (int q = threadIdx.x; q < hidden / 4; q += blockDim.x) {
+            float4 v = reinterpret_cast<const float4*>(in)[q];
+            float4 g = reinterpret_cast<const float4*>(gain)[q], b = reinterpret_cast<const float4*>(bias)[q];
+            store_quad(o + 4 * q, fmaf(tanhf(alpha * v.x), g.x, b.x), fmaf(tanhf(alpha * v.y), g.y, b.y),
+                       fmaf(tanhf(alpha * v.z), g.z, b.z), fmaf(tanhf(alpha * v.w), g.w, b.w));
+            if (o2) {
+                g = reinterpret_cast<const float4*>(gain2)[q];
+                b = reinterpret_cast<const float4*>(bias2)[q];
+                store_quad(o2 + 4 * q, fmaf(tanhf(alpha2 * v.x), g.x, b.x), fmaf(tanhf(alpha2 * v.y), g.y, b.y),
+                           fmaf(tanhf(alpha2 * v.z), g.z, b.z), fmaf(tanhf(alpha2 * v.w), g.w, b.w));
+            }
+        }
+    } else {
+        for (int e = threadIdx.x; e < hidden; e += blockDim.x) {
+            float v = in[e];
+            o[e] = from_float<TOut>(fmaf(tanhf(alpha * v), gain[e], bias[e]));
+            if (o2) o2[e] = from_float<TOut>(fmaf(tanhf(alpha2 * v), gain2[e], bias2[e]));
+        }
+    }
+}
+
+LLMB_EXPORT int llmb_tanh_norm(const float* x, const float* gain, const float* bias, float alpha, const int* rows,
+                               void* out, float alpha2, const float* gain2, const float* bias2, void* out2,
+                               int out_dtype, int n_rows, int hidden, cudaStream_t stream) {
+    if (n_rows == 0) return LLMB_OK;
+    LLMB_REQUIRE(n_rows > 0 && hidden > 0, "tanh_norm: bad sizes");
+    auto aligned = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    int vector = hidden % 4 == 0 && aligned(x) && aligned(gain) && aligned(bias) && aligned(out) &&
+                 (!gain2 || (aligned(gain2) && aligned(bias2) && aligned(out2)));
+    int threads = hidden >= 1024 ? 256 : 128;
+    if (out_dtype == LLMB_DTYPE_F32)
+        llmb::launch(tanh_norm_kernel<float>, n_rows, threads, 0, stream, true, x, rows, hidden, vector, alpha, gain, bias,
+                     (float*)out, alpha2, gain2, bias2, (float*)out2);
+    else if (out_dtype == LLMB_DTYPE_BF16)
+        llmb::launch(tanh_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, true, x, rows, hidden, vector, alpha, gain,
+                     bias, (__nv_bfloat16*)out, alpha2, gain2, bias2, (__nv_bfloat16*)out2);
+    else
+        return fail(LLMB_ERR_ARGUMENT, "tanh_norm: unknown dtype %d", out_dtype);
+    return check_launch("tanh_norm");
+}
+
 // ----------------------------------------------------------------------------- a norm's input without the norm
 // rows[t, :] = bfloat16(x[t, :]) and sumsq[t, 0] = sum of x[t, :]^2: what a product with a folded norm reads
 // (fusion.h) when no product's epilogue has left it. One block per row, the sum in a fixed order.
@@ -610,6 +668,7 @@ LLMB_EXPORT int llmb_random_normal(void* out, int dtype, long long n, unsigned l
 // the packed doors of the launching entry points (common.cuh)
 LLMB_PACKED(llmb_embed)
 LLMB_PACKED(llmb_rmsnorm)
+LLMB_PACKED(llmb_tanh_norm)
 LLMB_PACKED(llmb_cast_sumsq)
 LLMB_PACKED(llmb_scale_rows)
 LLMB_PACKED(llmb_rope_cache_write)

@@ -383,8 +383,9 @@ def rmsnorm(x, gain, eps, out_dtype, rows=None, out=None):
     return out
 
 
-def tanh_norm(x, alpha: float, gain, bias, out_dtype, rows=None, out=None):
-    """out[r, :] = tanh(alpha * x[rows[r] or r, :]) * gain + bias; x, gain and bias float32."""
+def tanh_norm(x, alpha: float, gain, bias, out_dtype, rows=None, out=None, second=None):
+    """out[r, :] = tanh(alpha * x[rows[r] or r, :]) * gain + bias; x, gain and bias float32. `second`
+    (alpha, gain, bias, out): a second norm of the same rows, written by the same launch."""
     _require_cuda(x, gain, bias, rows)
     hidden = x.shape[-1]
     n = rows.numel() if rows is not None else x.shape[0]
@@ -394,8 +395,15 @@ def tanh_norm(x, alpha: float, gain, bias, out_dtype, rows=None, out=None):
     _check_out(out, (n, hidden), out_dtype, "tanh_norm")
     if out is None:
         out = torch.empty((n, hidden), dtype=out_dtype, device=x.device)
+    alpha2, gain2, bias2, out2 = second if second is not None else (0.0, None, None, None)
+    if second is not None:
+        _require_cuda(gain2, bias2, out2)
+        _check_out(out2, (n, hidden), out_dtype, "tanh_norm")
+        if gain2.dtype != torch.float32 or bias2.dtype != torch.float32 or gain2.numel() != hidden or bias2.numel() != hidden:
+            raise KernelError("tanh_norm: the second gain and bias must be float32 of x's width")
     _call("elementwise", "llmb_tanh_norm", _ptr(x), _ptr(gain), _ptr(bias), _c_float(alpha), _ptr(rows), _ptr(out),
-          _c_int(_code(out_dtype)), _c_int(n), _c_int(hidden), _stream())
+          _c_float(alpha2), _ptr(gain2), _ptr(bias2), _ptr(out2), _c_int(_code(out_dtype)), _c_int(n), _c_int(hidden),
+          _stream())
     return out
 
 
@@ -441,8 +449,8 @@ def norm_rope_cache_write(u, q_width, k_width, v_width, q_gain, k_gain, eps, rop
           _c_int(q_width), _c_int(k_width), _c_int(v_width), _ptr(q_gain), _ptr(k_gain), _c_float(eps),
           _ptr(rope_table), _c_int(n_rot), _c_int(rot_unit), _c_int(1 if interleaved else 0), _ptr(tok_pos),
           _ptr(tok_seq), _ptr(q_out), _c_int(q_out.stride(0)), _ptr(block_table), _c_int(block_table.shape[1]),
-          _c_int(ring_pages), _ptr(k_cache), _ptr(v_cache if v_width else None), _c_int(1 if write_cache else 0),
-          _c_int(n), _stream())
+          _c_int(ring_pages), _ptr(k_cache), _c_int(k_cache.shape[1]), _ptr(v_cache if v_width else None),
+          _c_int(v_cache.shape[1] if v_width else 0), _c_int(1 if write_cache else 0), _c_int(n), _stream())
     return q_out
 
 

@@ -157,9 +157,12 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
     return result.to(qkv.dtype)
 
 
-def tanh_norm(x, alpha, gain, bias, out_dtype, rows=None, out=None):
+def tanh_norm(x, alpha, gain, bias, out_dtype, rows=None, out=None, second=None):
     if rows is not None:
         x = x[rows.long()]
+    if second is not None:
+        alpha2, gain2, bias2, out2 = second
+        out2.copy_((torch.tanh(x.to(torch.float32) * alpha2) * gain2 + bias2).to(out_dtype))
     y = (torch.tanh(x.to(torch.float32) * alpha) * gain + bias).to(out_dtype)
     if out is not None:
         out.copy_(y)
