@@ -816,7 +816,8 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
     cache may be the key cache itself (a mixer whose values are its keys)."""
     _require_cuda(qkv, k_cache, v_cache, block_table, tok_pos, tok_seq, sinks, gate)
     n = qkv.shape[0]
-    extras = sinks is not None or gate is not None or out_scale != 1.0
+    extras = (sinks is not None or gate is not None or out_scale != 1.0
+              or (out is not None and not out.is_contiguous()))
     if extras:
         if out is not None:
             _check_rows(out, n, n_heads * head_dim, qkv.dtype, "attention: out")

@@ -284,15 +284,19 @@ class ParallelBlock(Block):
             if views is not None:
                 views.prefix = prefix
 
+        # the feed-forward's own norm reads the same x as the mixer's: before the mixer adds into it
         if self.folded:
             if normed is None:
                 normed = ops.cast_sumsq(x, self.input_emit(ctx, n, x.device))
-            h = ops.FoldedNorm(normed.rows, normed.sumsq, normed.parts, self.spec.norm.eps, self.spec.norm.size)
+            h = h_ffn = ops.FoldedNorm(normed.rows, normed.sumsq, normed.parts, self.spec.norm.eps, self.spec.norm.size)
+        elif self.ffn_norm is not None and type(self.ffn_norm) is type(self.norm) and hasattr(self.norm, "forward_with"):
+            h, h_ffn = self.norm.forward_with(self.ffn_norm, x, ctx.dtype,
+                                              out=ctx.scratch("h_block", tuple(x.shape), ctx.dtype),
+                                              out_other=ctx.scratch("h_ffn", tuple(x.shape), ctx.dtype))
         else:
-            h = self.norm.forward(x, ctx.dtype, out=ctx.scratch("h_block", tuple(x.shape), ctx.dtype))
-        # the feed-forward's own norm reads the same x as the mixer's: before the mixer adds into it
-        h_ffn = h if self.ffn_norm is None else self.ffn_norm.forward(
-            x, ctx.dtype, out=ctx.scratch("h_ffn", tuple(x.shape), ctx.dtype))
+            h = h_ffn = self.norm.forward(x, ctx.dtype, out=ctx.scratch("h_block", tuple(x.shape), ctx.dtype))
+            if self.ffn_norm is not None:
+                h_ffn = self.ffn_norm.forward(x, ctx.dtype, out=ctx.scratch("h_ffn", tuple(x.shape), ctx.dtype))
         last = self.feed_forward if self.feed_forward is not None else self.mixer
         prefixed("mixer.")
         if last is self.mixer and emit_next is not None and self.mixer.emits:

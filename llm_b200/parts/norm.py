@@ -72,5 +72,13 @@ class TanhNorm(Norm):
     def forward(self, x, out_dtype, rows=None, out=None):
         return ops.tanh_norm(x, self.alpha, self.gain, self.bias, out_dtype, rows, out=out)
 
+    def forward_with(self, other, x, out_dtype, out=None, out_other=None):
+        """This norm and `other` (a TanhNorm too) of the same x in one launch: x is read once."""
+        if out_other is None:
+            out_other = torch.empty(tuple(x.shape), dtype=out_dtype, device=x.device)
+        first = ops.tanh_norm(x, self.alpha, self.gain, self.bias, out_dtype, out=out,
+                              second=(other.alpha, other.gain, other.bias, out_other))
+        return first, out_other
+
 
 register_norm("tanh_norm", TanhNorm)

@@ -102,7 +102,7 @@ def write_safetensors(path, tensors: dict, metadata: dict | None = None) -> None
         out.write(blob)
         for name in order:
             t = tensors[name].detach().cpu().contiguous()
-            out.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            out.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")     # (a scalar has no axis to view)
 
 
 def open_checkpoint(folder) -> dict:

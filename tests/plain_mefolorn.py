@@ -186,7 +186,7 @@ def norm_of(x, w, name):
 def forward(config, w, tokens, streams=None):
     """Logits [T, vocab] of a whole sequence. `streams` (a list) receives x after every layer."""
     eps = config["norm"]["eps"]
-    x = w["embed"][torch.tensor(tokens, dtype=torch.long)] * config["embedding"]["scale"]
+    x = w["embed"][torch.tensor(tokens, dtype=torch.long)] * (config.get("embedding") or {}).get("scale", 1.0)
     for i, layer in enumerate(config["layers"]):
         update = mixer(norm_of(x, w, f"l{i}.norm1"), w, f"l{i}.mix.", layer, eps)
         if layer.get("mlp"):
