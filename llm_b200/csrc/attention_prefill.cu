@@ -22,8 +22,16 @@
 //   the pages that cross a warp's diagonal are masked element by element, and
 //   pages wholly above it are skipped by that warp.
 //
-// Refused (the generic kernel serves them): windows, 32-bit caches, head sizes
-// other than 32, 64, 96, 128.
+// * with a window w a query at position p sees the keys j with p - w < j <= p: a tile starts at the
+//   page of its first query's oldest visible key (pages before it are neither read nor needed: they
+//   may have left a ring of pages), the pages that cross a row's lower edge are masked element by
+//   element, and a row whose first pages hold nothing it sees keeps a maximum of -inf without NaN.
+// * optional, all in the epilogue and in 32-bit: `sinks` [heads] (e^sink joins the head's
+//   denominator: no key, no value, not scaled), `gate` [T, heads] (the head's result times
+//   sigmoid(gate)), `out_scale`. When the value cache IS the key cache (a mixer whose cached rows
+//   serve as both), a page is fetched once and both products read the same tile.
+//
+// Refused (the generic kernel serves them): 32-bit caches, head sizes other than 32, 64, 96, 128.
 #include "common.cuh"
 #include "mma.cuh"
 
@@ -51,8 +59,10 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                          const int* __restrict__ block_table, int table_stride, int ring_pages,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_lens,
                          __nv_bfloat16* __restrict__ out, int out_stride, int n_heads,
-                         int n_kv_heads, float scale_log2) {
+                         int n_kv_heads, float scale_log2, int window, const float* __restrict__ sinks,
+                         const __nv_bfloat16* __restrict__ gate, int gate_stride, float out_scale) {
     constexpr int LDS = D + PAD;
+    const bool values_are_keys = k_cache == v_cache;
     constexpr int PAGE_ELEMS = LLMB_PAGE * LDS;
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* smem = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [STAGES][2][64][LDS]
@@ -74,6 +84,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     if (tile * BQ + warp * 16 >= n_new) warp_last_pos = -1;    // no query in this warp: skip every page
     int tile_last_pos = start + min(tile * BQ + BQ - 1, n_new - 1);
     int n_pages = tile_last_pos / LLMB_PAGE + 1;
+    // with a window: the oldest key that the tile's first query sees, and this warp's first query
+    int tile_oldest = window > 0 ? max(start + tile * BQ - window + 1, 0) : 0;
+    int first_page = tile_oldest / LLMB_PAGE;
+    int warp_oldest = window > 0 ? max(start + tile * BQ + warp * 16 - window + 1, 0) : 0;
+    int low0 = window > 0 ? pos0 - window + 1 : 0, low1 = window > 0 ? pos1 - window + 1 : 0;
 
     uint32_t qa[D / 16][4];
     {
@@ -98,7 +113,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         for (int c = tid; c < LLMB_PAGE * CHUNKS_PER_ROW; c += WARPS * 32) {
             int row = c / CHUNKS_PER_ROW, col = (c % CHUNKS_PER_ROW) * 8;
             cp_async16(ks + row * LDS + col, k_cache + base + (size_t)row * D + col);
-            cp_async16(vs + row * LDS + col, v_cache + base + (size_t)row * D + col);
+            if (!values_are_keys) cp_async16(vs + row * LDS + col, v_cache + base + (size_t)row * D + col);
         }
     };
 
@@ -109,18 +124,19 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
     float max0 = -INFINITY, max1 = -INFINITY, sum0 = 0.f, sum1 = 0.f;
 
-    load_page(0, 0);
+    load_page(first_page, first_page % STAGES);
     cp_async_commit();
-    for (int p = 0; p < n_pages; ++p) {
+    for (int p = first_page; p < n_pages; ++p) {
         cp_async_wait<0>();
         __syncthreads();                                // page p landed; everyone is done with page p - 1
         if (p + 1 < n_pages) load_page(p + 1, (p + 1) % STAGES);
         cp_async_commit();
         int key0 = p * LLMB_PAGE;
         if (key0 > warp_last_pos) continue;             // wholly above this warp's diagonal
+        if (key0 + LLMB_PAGE <= warp_oldest) continue;  // wholly before this warp's windows
 
         const __nv_bfloat16* ks = smem + (size_t)(p % STAGES) * 2 * PAGE_ELEMS;
-        const __nv_bfloat16* vs = ks + PAGE_ELEMS;
+        const __nv_bfloat16* vs = values_are_keys ? ks : ks + PAGE_ELEMS;
         float s[8][4];
 #pragma unroll
         for (int nb = 0; nb < 8; ++nb)
@@ -142,15 +158,17 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         // Maxima are kept on the raw scores (the scale is positive); the scale and log2(e) are
         // applied inside the exponent with one fused multiply-add per score.
         bool diagonal = key0 + LLMB_PAGE - 1 > start + tile * BQ + warp * 16;   // some key may be hidden
+        // with a window: some key may lie before the window of the warp's LAST row (the highest lower edge)
+        bool lower = window > 0 && key0 < start + tile * BQ + warp * 16 + 15 - window + 1;
         float local0 = -INFINITY, local1 = -INFINITY;
 #pragma unroll
         for (int nb = 0; nb < 8; ++nb) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                if (diagonal) {
+                if (diagonal || lower) {
                     int key = key0 + nb * 8 + 2 * t + i;
-                    if (key > pos0) s[nb][i] = -INFINITY;
-                    if (key > pos1) s[nb][2 + i] = -INFINITY;
+                    if (key > pos0 || key < low0) s[nb][i] = -INFINITY;
+                    if (key > pos1 || key < low1) s[nb][2 + i] = -INFINITY;
                 }
                 local0 = fmaxf(local0, s[nb][i]);
                 local1 = fmaxf(local1, s[nb][2 + i]);
@@ -160,12 +178,14 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         local0 = fmaxf(local0, __shfl_xor_sync(0xffffffffu, local0, 2));
         local1 = fmaxf(local1, __shfl_xor_sync(0xffffffffu, local1, 1));
         local1 = fmaxf(local1, __shfl_xor_sync(0xffffffffu, local1, 2));
-        // key 0 is visible to every row, so after page 0 both maxima are finite
+        // Without a window key 0 is visible to every row, so after page 0 both maxima are finite. With one, a
+        // row may have seen nothing yet: its maximum stays -inf, and a reference of 0 keeps every term 0.
         float new0 = fmaxf(max0, local0), new1 = fmaxf(max1, local1);
-        float rescale0 = fast_exp2((max0 - new0) * scale_log2), rescale1 = fast_exp2((max1 - new1) * scale_log2);
+        float ref0 = new0 == -INFINITY ? 0.f : new0, ref1 = new1 == -INFINITY ? 0.f : new1;
+        float rescale0 = fast_exp2((max0 - ref0) * scale_log2), rescale1 = fast_exp2((max1 - ref1) * scale_log2);
         max0 = new0;
         max1 = new1;
-        float shift0 = new0 * scale_log2, shift1 = new1 * scale_log2;
+        float shift0 = ref0 * scale_log2, shift1 = ref1 * scale_log2;
         float add0 = 0.f, add1 = 0.f;
 #pragma unroll
         for (int nb = 0; nb < 8; ++nb) {
@@ -207,7 +227,26 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
     sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
     sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
-    float inv0 = 1.0f / sum0, inv1 = 1.0f / sum1;
+    // sum and acc of a row are relative to e^(max * scale). A sink joins the denominator; where it exceeds
+    // the row's maximum it becomes the reference, so that nothing overflows.
+    float inv0, inv1;
+    if (sinks) {
+        float sink2 = sinks[head] * 1.4426950408889634f;
+        float m0 = max0 * scale_log2, m1 = max1 * scale_log2;
+        float r0 = fmaxf(m0, sink2), r1 = fmaxf(m1, sink2);
+        float w0 = fast_exp2(m0 - r0), w1 = fast_exp2(m1 - r1);
+        inv0 = w0 / (sum0 * w0 + fast_exp2(sink2 - r0));
+        inv1 = w1 / (sum1 * w1 + fast_exp2(sink2 - r1));
+    } else {
+        inv0 = 1.0f / sum0;
+        inv1 = 1.0f / sum1;
+    }
+    inv0 *= out_scale;
+    inv1 *= out_scale;
+    if (gate) {
+        if (row0 < n_new) inv0 *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)(first_token + row0) * gate_stride + head])));
+        if (row1 < n_new) inv1 *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)(first_token + row1) * gate_stride + head])));
+    }
     __nv_bfloat16* o0 = out + (size_t)(first_token + row0) * out_stride + (size_t)head * D;
     __nv_bfloat16* o1 = out + (size_t)(first_token + row1) * out_stride + (size_t)head * D;
 #pragma unroll
@@ -223,7 +262,8 @@ template <int D>
 static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                   const int* block_table, int table_stride, int ring_pages, const int* cu_seqlens,
                   const int* seq_lens, void* out, int out_stride, int n_seqs, int max_new, int n_heads,
-                  int n_kv_heads, float scale, cudaStream_t stream) {
+                  int n_kv_heads, float scale, int window, const float* sinks, const void* gate, int gate_stride,
+                  float out_scale, cudaStream_t stream) {
     constexpr int LDS = D + PAD;
     size_t smem = (size_t)STAGES * 2 * LLMB_PAGE * LDS * sizeof(__nv_bfloat16);
     static bool configured = false;
@@ -236,12 +276,13 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     attention_prefill_kernel<D><<<grid, WARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
         block_table, table_stride, ring_pages, cu_seqlens, seq_lens, (__nv_bfloat16*)out, out_stride,
-        n_heads, n_kv_heads, scale * 1.4426950408889634f);
+        n_heads, n_kv_heads, scale * 1.4426950408889634f, window, sinks, (const __nv_bfloat16*)gate, gate_stride,
+        out_scale);
     return check_launch("attention_prefill");
 }
 
 LLMB_EXPORT int llmb_attention_prefill_supports(int n_heads, int n_kv_heads, int head_dim, int window) {
-    LLMB_REQUIRE(window == 0, "attention_prefill: a window of %d is not served", window);
+    LLMB_REQUIRE(window >= 0, "attention_prefill: a window of %d", window);
     LLMB_REQUIRE(n_kv_heads > 0 && n_heads % n_kv_heads == 0,
                  "attention_prefill: %d heads are no multiple of %d kv heads", n_heads, n_kv_heads);
     LLMB_REQUIRE(head_dim == 32 || head_dim == 64 || head_dim == 96 || head_dim == 128,
@@ -257,7 +298,8 @@ LLMB_EXPORT int llmb_attention_prefill(const void* q, int q_stride, const void* 
                                        int ring_pages, const int* cu_seqlens, const int* seq_lens,
                                        void* out, int out_stride, int n_seqs, int max_new,
                                        int n_heads, int n_kv_heads, int head_dim, float scale,
-                                       int window, cudaStream_t stream) {
+                                       int window, const float* sinks, const void* gate, int gate_stride,
+                                       float out_scale, cudaStream_t stream) {
     if (n_seqs == 0 || max_new == 0) return LLMB_OK;
     int code = llmb_attention_prefill_supports(n_heads, n_kv_heads, head_dim, window);
     if (code) return code;
@@ -266,7 +308,8 @@ LLMB_EXPORT int llmb_attention_prefill(const void* q, int q_stride, const void* 
                  (reinterpret_cast<uintptr_t>(out) & 3) == 0,
                  "attention_prefill: q and out must be 4-byte aligned with even row strides");
 #define ARGS q, q_stride, k_cache, v_cache, block_table, table_stride, ring_pages, cu_seqlens, seq_lens, \
-             out, out_stride, n_seqs, max_new, n_heads, n_kv_heads, scale, stream
+             out, out_stride, n_seqs, max_new, n_heads, n_kv_heads, scale, window, sinks, gate, gate_stride, \
+             out_scale, stream
     switch (head_dim) {
         case 32: return launch<32>(ARGS);
         case 64: return launch<64>(ARGS);

@@ -833,7 +833,12 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
                                        cu_seqlens is not None and seq_lens is not None,
                                        qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0)
     if extras and variant not in _ATTENTION_WITH_EXTRAS:
+        # the next choice that takes a sink, a gate, a scale and rows inside a wider buffer
         variant = "attention_generic"
+        if not tactics.is_disabled("attention_prefill") and qkv.dtype == torch.bfloat16 and head_dim in (32, 64, 96, 128) \
+                and cu_seqlens is not None and seq_lens is not None and qkv.stride(0) % 2 == 0 and out.stride(0) % 2 == 0 \
+                and qkv.data_ptr() % 4 == 0 and out.data_ptr() % 4 == 0:
+            variant = "attention_prefill"
     if variant == "attention_prefill_tc":
         _call("attention_prefill_tc", "llmb_attention_prefill_tc", _ptr(qkv), _c_int(qkv.stride(0)),
               _c_int(n), _ptr(k_cache), _ptr(v_cache), _c_int(k_cache.shape[0]), _ptr(block_table),
@@ -846,7 +851,8 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
               _c_int(ring_pages), _ptr(cu_seqlens), _ptr(seq_lens), _ptr(out), _c_int(out.stride(0)),
               _c_int(cu_seqlens.numel() - 1), _c_int(max_new), _c_int(n_heads), _c_int(n_kv_heads),
-              _c_int(head_dim), _c_float(scale), _c_int(window), _stream())
+              _c_int(head_dim), _c_float(scale), _c_int(window), _ptr(sinks), _ptr(gate),
+              _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _stream())
     elif variant == "attention_decode":
         splits = decode_splits(n, n_kv_heads, max_len)
         lib = load_library("attention_decode")
@@ -881,7 +887,7 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
 
 
 # the attention kernels that take a sink, a gate and a scale of the result
-_ATTENTION_WITH_EXTRAS = ("attention_generic",)
+_ATTENTION_WITH_EXTRAS = ("attention_generic", "attention_prefill")
 
 
 def attention_replay_key(step, n_kv_heads: int):

@@ -152,26 +152,58 @@ def _attention(fn, batch, heads, groups, dim, dtype, window, sinks, gated, share
     return out_wide
 
 
+class only_generic:
+    """Inside: the tensor-core attention kernels are switched off, so the generic ones run in bfloat16 too."""
+    NAMES = ("attention_prefill", "sigmoid_attention_tiles")
+
+    def __init__(self, on=True):
+        self.on = on
+
+    def __enter__(self):
+        from llm_b200.ops import tactics
+        if self.on:
+            for name in self.NAMES:
+                tactics.disable(name)
+
+    def __exit__(self, *error):
+        from llm_b200.ops import tactics
+        if self.on:
+            for name in self.NAMES:
+                tactics.enable(name)
+
+
+@pytest.mark.parametrize("generic", [False, True])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("case", [
     # heads, kv heads, head size, window, sink, gate, values are keys
     (4, 1, 64, 70, True, True, True), (3, 1, 9, 5, True, True, True), (8, 1, 32, 130, True, False, True),
     (2, 1, 34, 21, False, True, True), (4, 2, 16, 0, True, True, False), (2, 1, 320, 40, True, True, True),
-    (16, 1, 128, 64, True, True, True), (4, 1, 96, 1, True, True, True)])
-def test_attention_with_sink_gate_and_shared_values(dtype, case):
+    (16, 1, 128, 64, True, True, True), (4, 1, 96, 1, True, True, True), (4, 2, 64, 0, False, False, False),
+    (2, 1, 128, 300, True, True, True), (6, 3, 32, 63, False, True, False)])
+def test_attention_with_sink_gate_and_shared_values(dtype, case, generic):
     ops = _ops()
     heads, groups, dim, window, sinks, gated, shared = case
-    for lengths, new in BATCHES:
+    if generic and dtype == torch.float32:
+        pytest.skip("the 32-bit path is the generic kernel already")
+    for lengths, new in BATCHES + [([700, 64, 129], [700, 3, 129])]:
         batch = Batch(lengths, new, seed=3 + len(lengths))
-        got = _attention(ops.attention, batch, heads, groups, dim, dtype, window, sinks, gated, shared, 0.8)
+        with only_generic(generic):
+            got = _attention(ops.attention, batch, heads, groups, dim, dtype, window, sinks, gated, shared, 0.8)
         want = _attention(plain_ops.attention, batch, heads, groups, dim, dtype, window, sinks, gated, shared, 0.8)
         torch.cuda.synchronize()
         _close(got, want, dtype, (case, lengths))
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, "generic"])
 @pytest.mark.parametrize("decode", [False, True])
 def test_attention_planted_keys_sink_and_window_edges(dtype, decode):
+    generic = dtype == "generic"
+    dtype = torch.bfloat16 if generic else dtype
+    with only_generic(generic):
+        _attention_planted(dtype, decode)
+
+
+def _attention_planted(dtype, decode):
     """One key is made to stand out: the result is that key's row exactly when the key is inside the window,
     also far back, at page borders and at both edges; a sink that stands out takes all the weight."""
     ops = _ops()
@@ -232,20 +264,31 @@ def _sigmoid(fn, batch, heads, groups, dim, vdim, dtype, window, talk, bias, see
     (4, 2, 6, 10, 9, True, True), (2, 2, 8, 5, 33, True, True), (4, 2, 64, 32, 40, True, True),
     (4, 1, 32, 64, 100, True, True), (2, 1, 16, 24, 0, True, True), (3, 1, 20, 20, 7, False, True),
     (4, 4, 64, 64, 64, True, False), (8, 2, 128, 128, 200, True, True), (16, 4, 96, 96, 65, True, True)])
-def test_sigmoid_attention(dtype, case):
+@pytest.mark.parametrize("generic", [False, True])
+def test_sigmoid_attention(dtype, case, generic):
     ops = _ops()
     heads, groups, dim, vdim, window, talk, bias = case
-    for lengths, new in BATCHES:
+    if generic and dtype == torch.float32:
+        pytest.skip("the 32-bit path is the generic kernel already")
+    for lengths, new in BATCHES + [([700, 64, 129], [700, 3, 129])]:
         batch = Batch(lengths, new, seed=7 + len(lengths))
-        got = _sigmoid(ops.sigmoid_attention, batch, heads, groups, dim, vdim, dtype, window, talk, bias)
+        with only_generic(generic):
+            got = _sigmoid(ops.sigmoid_attention, batch, heads, groups, dim, vdim, dtype, window, talk, bias)
         want = _sigmoid(plain_ops.sigmoid_attention, batch, heads, groups, dim, vdim, dtype, window, talk, bias)
         torch.cuda.synchronize()
         _close(got, want, dtype, (case, lengths))
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, "generic"])
 @pytest.mark.parametrize("decode", [False, True])
 def test_sigmoid_attention_planted_keys_and_mixing(dtype, decode):
+    generic = dtype == "generic"
+    dtype = torch.bfloat16 if generic else dtype
+    with only_generic(generic):
+        _sigmoid_planted(dtype, decode)
+
+
+def _sigmoid_planted(dtype, decode):
     """With a bias far below zero no key has weight, except one whose score is made large: its value
     arrives exactly when it is inside the window. The key is seen by head 1 only; head 0 gets it
     through the mixing matrix alone."""

@@ -290,11 +290,11 @@ def test_an_engine_refuses_a_model_no_kernel_serves(tmp_path):
     from llm_b200.errors import LlmError
     from llm_b200.weights import write_random_model
     raw = dict(CONFIGS["A"][0])
-    raw["head_dim"] = 272
+    raw["head_dim"] = 528
     folder = tmp_path / "wide_heads"
     write_random_model(folder, config_from_dict(raw), 0, torch.bfloat16)
     for dtype in DTYPES:
-        with pytest.raises(LlmError, match="head_dim 272 exceeds 256"):
+        with pytest.raises(LlmError, match="head_dim 528 exceeds 512"):
             Engine(load_model(folder, dtype, DEV), max_tokens=256)
 
 

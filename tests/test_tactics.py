@@ -80,7 +80,7 @@ def test_refusals_name_the_assumption_that_fails():
     assert text.startswith("attention: attention_generic") and "head_dim 80" in text
     text = tactics.explain("attention", decode=True, dtype=BF16, n_heads=4, n_kv_heads=2, head_dim=64,
                            window=100, packed=True)
-    assert text.startswith("attention: attention_generic") and "no window" in text
+    assert text.startswith("attention: attention_prefill") and "no window" in text        # the flash kernel takes windows
     text = tactics.explain("linear", m=2048, n=4096, k=4100, in_dtype=BF16, out_dtype=BF16, lda=4100)
     assert text.startswith("linear: gemm_simt") and "multiple of 8" in text and "exceed 64" in text
 
