@@ -132,6 +132,26 @@ std::string sigmoid_generic_guard(const Shape& s) {
     return "";
 }
 
+bool sigmoid_tiles_shape(int dim, int vdim) {
+#define X(DK, DV) if (dim == DK && vdim == DV) return true;
+    LLMB_SIGMOID_SHAPES(X)
+#undef X
+    return false;
+}
+
+std::string sigmoid_tiles_guard(const Shape& s) {
+    if (!s.packed) return "needs the packed batch description (cu_seqlens and seq_lens)";
+    if (!s.bf16) return "bfloat16 caches only";
+    if (!sigmoid_tiles_shape(s.head_dim, s.value_dim))
+        return "head size " + std::to_string(s.head_dim) + " with value size " + std::to_string(s.value_dim) +
+               " (served: 32/32, 32/64, 64/32, 64/64, 64/128, 96/96, 128/64, 128/128)";
+    if (s.n_kv_heads * s.head_dim > LLMB_SIGMOID_MAX_MIXED)
+        return std::to_string(s.n_kv_heads) + " key heads of " + std::to_string(s.head_dim) + ": a mixed query of more than " +
+               std::to_string(LLMB_SIGMOID_MAX_MIXED) + " elements does not fit in shared memory beside the tiles";
+    if (!s.aligned) return "the queries' or the result's rows are not 4-byte aligned";
+    return "";
+}
+
 const std::vector<Row>& table(int family) {
     static const std::vector<Row> linear = {
         {"gemm_tc", 30, tc_guard,
@@ -179,6 +199,11 @@ const std::vector<Row>& table(int family) {
          "up to 256, any group, window and kept first tokens; the only variant of the 32-bit path"},
     };
     static const std::vector<Row> sigmoid_attention = {
+        {"sigmoid_attention_tiles", 10, sigmoid_tiles_guard,
+         "tiles of 64 queries of one head on mma.sync over the pages the tile's windows reach; the mix over the heads "
+         "is done on the queries (a mixed query of kv heads x head size elements in shared memory), the key tiles of "
+         "all kv heads and the group's value tile run through a ring of three buffers, weights in 32-bit; also serves "
+         "steps of one token a sequence"},
         {"sigmoid_attention_generic", 0, sigmoid_generic_guard,
          "one block per (token, head): the scores of all heads for a key, mixed over the heads, sigmoid weights, "
          "32-bit arithmetic, any sizes up to 256, up to 128 heads, any group and window; the only variant of the "

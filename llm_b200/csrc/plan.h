@@ -9,3 +9,7 @@
 #define LLMB_MAX_HEAD_DIM 256   // largest head size any attention kernel takes
 // The (map size, value size) pairs the tensor-core kernels of the differential attention are built for.
 #define LLMB_DIFF_SHAPES(X) X(32, 32) X(32, 64) X(48, 96) X(64, 64) X(64, 128) X(128, 128)
+// The (head size, value size) pairs the tensor-core kernel of the sigmoid attention is built for.
+#define LLMB_SIGMOID_SHAPES(X) X(32, 32) X(32, 64) X(64, 32) X(64, 64) X(64, 128) X(96, 96) X(128, 64) X(128, 128)
+// The widest mixed query (key/value heads times head size) that kernel keeps in shared memory.
+#define LLMB_SIGMOID_MAX_MIXED 1024

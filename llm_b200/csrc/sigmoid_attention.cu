@@ -16,7 +16,22 @@
 // sum; the four partial sums are added in a fixed order. Which keys a query sees and the order in which they
 // are reduced depend only on its position and the window, so a token's result does not depend on the batch
 // or on how the tokens were cut into steps. Any head and value size up to 256, any group; both dtypes.
+//
+// sigmoid_attention_tiles (bfloat16, the head and value sizes of LLMB_SIGMOID_SHAPES): tiles of 64 queries
+// of one head on mma.sync, over the pages the tile's windows reach. The mix is linear in the queries, so it
+// is done on them: with G key/value heads, the mixed score of head a is
+//     sum over g of (sum over the heads b of group g of talk[a, b] q_b) . k_g,
+// one product of a "mixed query" of G * dim elements with the keys of all G heads at a position. A block
+// forms its tile's mixed queries once (32-bit sums, rounded to bfloat16 as any query is) in shared memory;
+// per page it runs the G key tiles and then the value tile of its own group through a ring of three
+// buffers (cp.async, two units in flight), S accumulating over the key tiles in 32-bit; the weights
+// sigmoid(scale S + bias) are formed in 32-bit, masked at the diagonal and at the window's lower edge, and
+// become the A operand of the second product. Nothing is normalised, so there is no running maximum and no
+// rescaling. Without a matrix the mixed query is the head's own and G is 1. The price of mixing is G times
+// the score products of a plain attention; a step in which every sequence brings one token runs the same
+// kernel with one live row a tile.
 #include "common.cuh"
+#include "mma.cuh"
 
 using namespace llmb;
 
@@ -139,4 +154,246 @@ LLMB_EXPORT int llmb_sigmoid_attention_generic(const void* q, int q_stride, cons
     return check_launch("sigmoid_attention_generic");
 }
 
+// ----------------------------------------------------------------------------- tiles on the tensor cores
+
+constexpr int BQ = WARPS * 16;               // queries per block
+constexpr int STAGES = 3;
+constexpr int PAD = 8;
+
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int D, int DV>
+__global__ void __launch_bounds__(WARPS * 32)
+sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
+                               const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
+                               int table_stride, int ring_pages, const int* __restrict__ cu_seqlens,
+                               const int* __restrict__ seq_lens, __nv_bfloat16* __restrict__ out, int out_stride,
+                               int n_heads, int n_kv_heads, float scale, int window, const float* __restrict__ talk,
+                               const float* __restrict__ head_bias, float out_scale) {
+    constexpr int LDS = (D > DV ? D : DV) + PAD;
+    constexpr int TILE_ELEMS = LLMB_PAGE * LDS;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    int seq = blockIdx.z, head = blockIdx.x;
+    int first_token = cu_seqlens[seq];
+    int n_new = cu_seqlens[seq + 1] - first_token;
+    int n_tiles = (n_new + BQ - 1) / BQ;
+    if ((int)blockIdx.y >= n_tiles) return;
+    int tile = n_tiles - 1 - blockIdx.y;
+    int start = seq_lens[seq] - n_new;
+    int group = n_heads / n_kv_heads;
+    int kv_head = head / group;
+    int g_first = talk ? 0 : kv_head, g_count = talk ? n_kv_heads : 1;     // the key heads whose scores enter
+    int ldq = g_count * D + PAD;
+    __nv_bfloat16* mixed = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [BQ][ldq]
+    __nv_bfloat16* ring = mixed + (size_t)BQ * ldq;                         // [STAGES][64][LDS]
+    int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int* pages = block_table + (size_t)seq * table_stride;
+
+    int row0 = tile * BQ + warp * 16 + g, row1 = row0 + 8;
+    int pos0 = start + row0, pos1 = start + row1;
+    int warp_last_pos = start + min(tile * BQ + warp * 16 + 15, n_new - 1);
+    if (tile * BQ + warp * 16 >= n_new) warp_last_pos = -1;
+    int tile_last_pos = start + min(tile * BQ + BQ - 1, n_new - 1);
+    int n_pages = tile_last_pos / LLMB_PAGE + 1;
+    int tile_oldest = window > 0 ? max(start + tile * BQ - window + 1, 0) : 0;
+    int first_page = tile_oldest / LLMB_PAGE;
+    int warp_oldest = window > 0 ? max(start + tile * BQ + warp * 16 - window + 1, 0) : 0;
+    int low0 = window > 0 ? pos0 - window + 1 : 0, low1 = window > 0 ? pos1 - window + 1 : 0;
+
+    int units_per_page = g_count + 1;
+    int n_units = (n_pages - first_page) * units_per_page;
+    auto load_unit = [&](int n) {
+        int p = first_page + n / units_per_page, i = n % units_per_page;
+        size_t page = (size_t)pages[p % ring_pages];
+        __nv_bfloat16* to = ring + (size_t)(n % STAGES) * TILE_ELEMS;
+        if (i < g_count) {
+            const __nv_bfloat16* from = k_cache + ((page * n_kv_heads + g_first + i) * LLMB_PAGE) * D;
+            for (int c = tid; c < LLMB_PAGE * (D / 8); c += WARPS * 32) {
+                int row = c / (D / 8), col = (c % (D / 8)) * 8;
+                cp_async16(to + row * LDS + col, from + (size_t)row * D + col);
+            }
+        } else {
+            const __nv_bfloat16* from = v_cache + ((page * n_kv_heads + kv_head) * LLMB_PAGE) * DV;
+            for (int c = tid; c < LLMB_PAGE * (DV / 8); c += WARPS * 32) {
+                int row = c / (DV / 8), col = (c % (DV / 8)) * 8;
+                cp_async16(to + row * LDS + col, from + (size_t)row * DV + col);
+            }
+        }
+    };
+    if (n_units > 0) load_unit(0);
+    cp_async_commit();
+    if (n_units > 1) load_unit(1);
+    cp_async_commit();
+
+    // the tile's mixed queries: for key head g, sum over the heads b of its group of talk[head, b] * q_b
+    {
+        int pairs = g_count * D / 2;
+        for (int idx = tid; idx < BQ * pairs; idx += WARPS * 32) {
+            int r = idx / pairs, c = (idx % pairs) * 2;
+            int gi = c / D, d = c % D;
+            int row = tile * BQ + r;
+            float lo = 0.f, hi = 0.f;
+            if (row < n_new) {
+                const __nv_bfloat16* q_row = q + (size_t)(first_token + row) * q_stride;
+                if (talk) {
+                    for (int b = 0; b < group; ++b) {
+                        int other = (g_first + gi) * group + b;
+                        float w = talk[(size_t)head * n_heads + other];
+                        lo = fmaf(w, to_float(q_row[(size_t)other * D + d]), lo);
+                        hi = fmaf(w, to_float(q_row[(size_t)other * D + d + 1]), hi);
+                    }
+                } else {
+                    lo = to_float(q_row[(size_t)head * D + d]);
+                    hi = to_float(q_row[(size_t)head * D + d + 1]);
+                }
+            }
+            *reinterpret_cast<__nv_bfloat162*>(mixed + (size_t)r * ldq + c) = __floats2bfloat162_rn(lo, hi);
+        }
+    }
+    float bias = head_bias ? head_bias[head] : 0.f;
+    // sigmoid(z) = 1 / (1 + 2^(-z log2 e)), z = scale * s + bias
+    float slope = -scale * 1.4426950408889634f, offset = -bias * 1.4426950408889634f;
+
+    float acc[DV / 8][4];
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
+    float s[8][4];
+
+    for (int n = 0; n < n_units; ++n) {
+        cp_async_wait<1>();
+        __syncthreads();                    // unit n landed (and, at n = 0, the mixed queries); all are done with unit n - 1
+        if (n + 2 < n_units) load_unit(n + 2);
+        cp_async_commit();
+        int p = first_page + n / units_per_page, i = n % units_per_page;
+        int key0 = p * LLMB_PAGE;
+        if (key0 > warp_last_pos || key0 + LLMB_PAGE <= warp_oldest) continue;     // nothing of this page for this warp
+        const __nv_bfloat16* tile_s = ring + (size_t)(n % STAGES) * TILE_ELEMS;
+        if (i == 0) {
+#pragma unroll
+            for (int nb = 0; nb < 8; ++nb)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[nb][e] = 0.f;
+        }
+        if (i < g_count) {
+            const __nv_bfloat16* a_base = mixed + (size_t)(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldq + i * D + (lane >> 4) * 8;
+#pragma unroll
+            for (int kstep = 0; kstep < D / 16; ++kstep) {
+                uint32_t a[4];
+                ldmatrix_x4(a, a_base + kstep * 16);
+#pragma unroll
+                for (int nb = 0; nb < 8; nb += 2) {
+                    uint32_t b[4];
+                    int row = nb * 8 + (lane >> 4) * 8 + (lane & 7);
+                    int col = kstep * 16 + ((lane >> 3) & 1) * 8;
+                    ldmatrix_x4(b, tile_s + row * LDS + col);
+                    mma_bf16(s[nb], a[0], a[1], a[2], a[3], b[0], b[1]);
+                    mma_bf16(s[nb + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
+                }
+            }
+            continue;
+        }
+        // the value tile: weights from the finished scores, then O += W V
+        bool edge = key0 + LLMB_PAGE - 1 > start + tile * BQ + warp * 16 ||
+                    (window > 0 && key0 < start + tile * BQ + warp * 16 + 15 - window + 1);
+#pragma unroll
+        for (int nb = 0; nb < 8; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float w0 = __frcp_rn(1.0f + fast_exp2(fmaf(s[nb][e], slope, offset)));
+                float w1 = __frcp_rn(1.0f + fast_exp2(fmaf(s[nb][2 + e], slope, offset)));
+                if (edge) {
+                    int key = key0 + nb * 8 + 2 * t + e;
+                    if (key > pos0 || key < low0) w0 = 0.f;
+                    if (key > pos1 || key < low1) w1 = 0.f;
+                }
+                s[nb][e] = w0;
+                s[nb][2 + e] = w1;
+            }
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+            uint32_t pa0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+            uint32_t pa1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+            uint32_t pa2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+            uint32_t pa3 = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < DV / 8; n2 += 2) {
+                uint32_t b[4];
+                int row = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                int col = (n2 + (lane >> 4)) * 8;
+                ldmatrix_x4_trans(b, tile_s + row * LDS + col);
+                mma_bf16(acc[n2], pa0, pa1, pa2, pa3, b[0], b[1]);
+                mma_bf16(acc[n2 + 1], pa0, pa1, pa2, pa3, b[2], b[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    __nv_bfloat16* o0 = out + (size_t)(first_token + row0) * out_stride + (size_t)head * DV;
+    __nv_bfloat16* o1 = out + (size_t)(first_token + row1) * out_stride + (size_t)head * DV;
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) {
+        if (row0 < n_new)
+            *reinterpret_cast<__nv_bfloat162*>(o0 + n * 8 + 2 * t) = __floats2bfloat162_rn(acc[n][0] * out_scale, acc[n][1] * out_scale);
+        if (row1 < n_new)
+            *reinterpret_cast<__nv_bfloat162*>(o1 + n * 8 + 2 * t) = __floats2bfloat162_rn(acc[n][2] * out_scale, acc[n][3] * out_scale);
+    }
+}
+
+template <int D, int DV>
+static int launch_tiles(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
+                        int table_stride, int ring_pages, const int* cu_seqlens, const int* seq_lens, void* out,
+                        int out_stride, int n_seqs, int max_new, int n_heads, int n_kv_heads, float scale, int window,
+                        const float* talk, const float* head_bias, float out_scale, cudaStream_t stream) {
+    constexpr int LDS = (D > DV ? D : DV) + PAD;
+    int g_count = talk ? n_kv_heads : 1;
+    size_t smem = sizeof(__nv_bfloat16) * ((size_t)BQ * (g_count * D + PAD) + (size_t)STAGES * LLMB_PAGE * LDS);
+    LLMB_REQUIRE(smem <= 220 * 1024, "sigmoid_attention_tiles: %d key heads of %d do not fit in shared memory", g_count, D);
+    static size_t configured = 0;
+    if (smem > configured) {
+        LLMB_CUDA(cudaFuncSetAttribute(sigmoid_attention_tiles_kernel<D, DV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem));
+        configured = smem;
+    }
+    dim3 grid(n_heads, (max_new + BQ - 1) / BQ, n_seqs);
+    sigmoid_attention_tiles_kernel<D, DV><<<grid, WARPS * 32, smem, stream>>>(
+        (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
+        table_stride, ring_pages, cu_seqlens, seq_lens, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale, window,
+        talk, head_bias, out_scale);
+    return check_launch("sigmoid_attention_tiles");
+}
+
+// q: the new tokens' queries, packed sequence after sequence; token i of sequence b is row cu_seqlens[b] + i and
+// stands at position seq_lens[b] - n_new(b) + i (seq_lens: the lengths after this step). max_new: the most new
+// tokens any sequence brings.
+LLMB_EXPORT int llmb_sigmoid_attention_tiles(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                             const int* block_table, int table_stride, int ring_pages,
+                                             const int* cu_seqlens, const int* seq_lens, void* out, int out_stride,
+                                             int n_seqs, int max_new, int n_heads, int n_kv_heads, int dim, int vdim,
+                                             float scale, int window, const float* talk, const float* head_bias,
+                                             float out_scale, cudaStream_t stream) {
+    if (n_seqs == 0 || max_new == 0) return LLMB_OK;
+    LLMB_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_heads <= 65535,
+                 "sigmoid_attention_tiles: %d heads are no multiple of %d kv heads", n_heads, n_kv_heads);
+    LLMB_REQUIRE(n_seqs <= 65535 && max_new / BQ < 65535 && ring_pages > 0 && window >= 0, "sigmoid_attention_tiles: bad sizes");
+    LLMB_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0 &&
+                 (reinterpret_cast<uintptr_t>(out) & 3) == 0,
+                 "sigmoid_attention_tiles: q and out must be 4-byte aligned with even row strides");
+#define X(DK, DVAL)                                                                                                  \
+    if (dim == DK && vdim == DVAL)                                                                                   \
+        return launch_tiles<DK, DVAL>(q, q_stride, k_cache, v_cache, block_table, table_stride, ring_pages, cu_seqlens, \
+                                      seq_lens, out, out_stride, n_seqs, max_new, n_heads, n_kv_heads, scale, window, \
+                                      talk, head_bias, out_scale, stream);
+    LLMB_SIGMOID_SHAPES(X)
+#undef X
+    return fail(LLMB_ERR_ARGUMENT, "sigmoid_attention_tiles: head size %d with value size %d is not built", dim, vdim);
+}
+
 LLMB_PACKED(llmb_sigmoid_attention_generic)
+LLMB_PACKED(llmb_sigmoid_attention_tiles)

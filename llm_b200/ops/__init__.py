@@ -923,6 +923,16 @@ def sigmoid_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok
         raise KernelError(f"sigmoid_attention: talk must be contiguous float32 [{n_heads}, {n_heads}]")
     if head_bias is not None and (head_bias.dtype != torch.float32 or head_bias.numel() != n_heads):
         raise KernelError(f"sigmoid_attention: head_bias must be float32 [{n_heads}]")
+    variant = tactics.choose_sigmoid_attention(
+        decode, q.dtype, n_heads, n_kv_heads, dim, vdim, window, cu_seqlens is not None and seq_lens is not None,
+        q.stride(0) % 2 == 0 and out.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0 and out.data_ptr() % 4 == 0)
+    if variant == "sigmoid_attention_tiles":
+        _call("sigmoid_attention", "llmb_sigmoid_attention_tiles", _ptr(q), _c_int(q.stride(0)), _ptr(k_cache),
+              _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(cu_seqlens),
+              _ptr(seq_lens), _ptr(out), _c_int(out.stride(0)), _c_int(cu_seqlens.numel() - 1), _c_int(max_new),
+              _c_int(n_heads), _c_int(n_kv_heads), _c_int(dim), _c_int(vdim), _c_float(scale), _c_int(window),
+              _ptr(talk), _ptr(head_bias), _c_float(out_scale), _stream())
+        return out
     _call("sigmoid_attention", "llmb_sigmoid_attention_generic", _ptr(q), _c_int(q.stride(0)), _ptr(k_cache),
           _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(tok_pos),
           _ptr(tok_seq), _ptr(out), _c_int(out.stride(0)), _c_int(_code(q.dtype)), _c_int(n), _c_int(n_heads),
