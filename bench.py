@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the library on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
-    python bench.py --workload llama-2-7b | llama-3.2-1b | 8b-decode512 | guberax
+    python bench.py --workload llama-2-7b | llama-3.2-1b | 8b-decode512 | guberax | mefolorn
 
 The default run has the layer sizes of a Llama-3.1-8B (32 layers, hidden 4096,
 32 heads over 8 kv heads of 128, feed-forward 14336, vocabulary 128256, llama3
@@ -13,7 +13,8 @@ baseline instead and prints its own line: a Llama-2-7B shape with 16 prompts of 
 tokens and 128 new tokens each, a Llama-3.2-1B shape with 64 prompts of 1 to 8,192 tokens and
 256 new tokens at temperature 0.7 (both through `LLM.generate`, host ids in and out), and the
 Llama-3.1-8B shape decoding 256 tokens after prompts of 512 at batch 1, 8 and 64; `guberax`
-times the Guberax architecture beside Llama at equal layer sizes. The test names follow the `pp`/`tg`
+times the Guberax architecture beside Llama at equal layer sizes, `mefolorn` the Mefolorn
+architecture beside both. The test names follow the `pp`/`tg`
 split of MythEclipse/llm's bench (apps/cli/src/bench.rs:10-12): prefill alone,
 and decoding alone on a cache that is already filled.
 """
@@ -337,8 +338,112 @@ def workload_guberax(args):
     return 0
 
 
+def workload_mefolorn(args):
+    """Mefolorn beside Guberax (the library's closest model: parallel blocks, windowed attention, a
+    convolution's state) and Llama at equal layer sizes (the Llama-3.1-8B and Llama-3.2-1B shapes), random
+    bfloat16 weights, `--layers` layers of each (at most 8) plus the head: prefill of 2,048 and 8,192 tokens
+    and decode at batch 8 and 64 over contexts of 2,048 and 8,192, timed with CUDA events, every step on the
+    device. Mefolorn and Guberax run with windows of 2,048; Mefolorn's layers alternate between its two
+    mixers. With LLMB_PROFILE=1 the library prints its per-kernel table for the same steps to standard error."""
+    import torch
+    from llm_b200 import ops
+    from llm_b200.config import config_from_dict
+    from llm_b200.engine import Engine, Entry, random_model
+    from llm_b200.shapes import shape
+
+    torch.cuda.set_device(0)
+    device = "cuda:0"
+    layers = min(args.layers, 8)
+    peak, peak_source = peaks()
+    clocks = ClockSampler()
+    clocks.start()
+
+    def time_decode(model, vocab, batch, context, steps, warmup):
+        per_seq = (context + 63) // 64 * 64
+        engine = Engine(model, max_tokens=batch * per_seq, max_seq_len=context, max_slots=batch)
+        for group in engine.cache.groups:
+            for tensor in (group.storage, group.keys, group.values if group.values is not group.keys else None):
+                if tensor is not None:
+                    flat = tensor.view(-1)
+                    for at in range(0, flat.numel(), 1 << 26):
+                        part = flat[at:at + (1 << 26)]
+                        part.copy_(torch.randn(part.numel(), device=device, dtype=torch.float32).mul_(0.5))
+        slots = engine.acquire(batch)
+        start = context - steps - warmup - 1
+        for s in slots:
+            engine.cache.reserve(s, start)
+            engine.cache.set_length(s, start)
+        feed = torch.randint(0, vocab, (steps + warmup, batch), generator=torch.Generator().manual_seed(batch)).tolist()
+        for k in range(warmup):
+            engine.step([Entry(s, [t], [0]) for s, t in zip(slots, feed[k])])
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for k in range(warmup, warmup + steps):
+            engine.step([Entry(s, [t], [0]) for s, t in zip(slots, feed[k])])
+        end.record()
+        torch.cuda.synchronize()
+        ms = begin.elapsed_time(end) / steps
+        engine.release(slots)
+        del engine
+        torch.cuda.empty_cache()
+        return ms
+
+    def time_prefill(model, vocab, n_tokens, repeats=3):
+        engine = Engine(model, max_tokens=n_tokens + 64, max_seq_len=n_tokens + 64, max_slots=1)
+        prompt = torch.randint(0, vocab, (n_tokens,), generator=torch.Generator().manual_seed(1)).tolist()
+        times = []
+        for k in range(3 + repeats):
+            (slot,) = engine.acquire()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            begin.record()
+            engine.step([Entry(slot, prompt, [n_tokens - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            if k >= 3:
+                times.append(begin.elapsed_time(end))
+            engine.release([slot])
+        del engine
+        torch.cuda.empty_cache()
+        return sum(times) / len(times)
+
+    steps, warmup = max(16, min(args.steps, 64)), max(args.warmup, 5)
+    rows = {}
+    sizes = [("1b", "llama-3.2-1b", "guberax-1b", "mefolorn-1b"), ("8b", "llama-3.1-8b", "guberax-8b", "mefolorn-8b")]
+    for size, llama_name, guberax_name, mefolorn_name in sizes:
+        arms = [("llama", shape(llama_name, layers)), ("guberax_window2048", shape(guberax_name, layers, 2048)),
+                ("mefolorn_window2048", shape(mefolorn_name, layers, 2048))]
+        for label, raw in arms:
+            config = config_from_dict(raw)
+            vocab = config.model_spec().vocab
+            model = random_model(config, seed=0, device=device)
+            out = {"weight_bytes": model.weight_bytes()}
+            for n in (2048, 8192):
+                ms = time_prefill(model, vocab, n)
+                out[f"prefill_{n}"] = {"ms": round(ms, 3), "tok_s": round(n * 1e3 / ms, 1)}
+            for batch in (8, 64):
+                for context in (2048, 8192):
+                    ms = time_decode(model, vocab, batch, context, steps, warmup)
+                    out[f"decode_b{batch}_c{context}"] = {"ms": round(ms, 4), "tok_s": round(batch * 1e3 / ms, 1)}
+            rows[f"{label}-{size}"] = out
+            del model
+            torch.cuda.empty_cache()
+    clocks.stop()
+    print(json.dumps({
+        "metric": "prefill and decode tokens/s, Mefolorn beside Guberax and Llama at equal layer sizes, bf16",
+        "value": rows["mefolorn_window2048-8b"]["decode_b8_c8192"]["tok_s"], "unit": "tokens/s", "n_gpus": 1,
+        "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "steps": steps, "warmup": warmup,
+        "config": {"layers": layers, "weights": "random N(0,0.02) seed 0", "peaks": peak_source,
+                   "sizes": "8b: width 4096, 32/8 heads of 128, ff 14336, latent 1536 / 128, recurrence 4096 in 16 blocks; "
+                            "1b: width 2048, 32/8 heads of 64, ff 8192, latent 768 / 128, recurrence 2048 in 16 blocks; "
+                            "vocabulary 128256; windows 2048"},
+        "rows": rows, "gpu_launches": ops.launch_count(), "clocks": clocks.summary()}))
+    return 0
+
+
 WORKLOADS = {"llama-2-7b": workload_llama_2_7b, "llama-3.2-1b": workload_llama_3_2_1b,
-             "8b-decode512": workload_8b_decode512, "guberax": workload_guberax}
+             "8b-decode512": workload_8b_decode512, "guberax": workload_guberax, "mefolorn": workload_mefolorn}
 
 
 

@@ -48,6 +48,27 @@ SHAPES["guberax-8b"] = _guberax(4096, 32, 8, 64, 128, 14336, 128256, 32, 1 << 20
 SHAPES["guberax-1b"] = _guberax(2048, 32, 8, 32, 64, 8192, 128256, 16, 1 << 20)
 
 
+def _mefolorn(width, heads, kv_heads, dim, ff, vocab, layers, window, q_rank, kv_rank, blocks):
+    """A Mefolorn configuration whose layers match a Llama shape in size (width, heads, head size, feed-forward,
+    vocabulary): layers alternate between the side-by-side mixer (sigmoid attention with the Llama shape's heads;
+    a gated recurrence as wide as the model) and the latent attention (the same heads over a cached latent of
+    `kv_rank`)."""
+    pair = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                     "mask": {"size": window}, "rot": {"base": 500000.0, "dims": dim}},
+            "right": {"width": width, "blocks": blocks, "conv": 4}, "left_scale": 0.6, "right_scale": 0.9}
+    latent = {"heads": heads, "dim": dim, "vdim": dim, "q_rank": q_rank, "kv_rank": kv_rank, "scale": dim ** -0.5,
+              "mask": {"size": window}}
+    kinds = [{"type": "parallel", "mixer": pair, "mlp": {"kind": "dense", "ff": ff}},
+             {"type": "latent_attention", "mixer": latent, "mlp": {"kind": "dense", "ff": ff}}]
+    return {"architecture": "Mefolorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": [kinds[i % 2] for i in range(layers)]}
+
+
+# the layer sizes of llama-3.1-8b and llama-3.2-1b; windows of 2,048 unless a run sets another
+SHAPES["mefolorn-8b"] = _mefolorn(4096, 32, 8, 128, 14336, 128256, 32, 2048, 1536, 128, 16)
+SHAPES["mefolorn-1b"] = _mefolorn(2048, 32, 8, 64, 8192, 128256, 16, 2048, 768, 128, 16)
+
+
 def shape(name: str, layers: int | None = None, window: int | None = None) -> dict:
     """A copy of the named shape's config.json, optionally with fewer layers (and, for a shape
     with windowed attention, another window)."""
@@ -57,11 +78,13 @@ def shape(name: str, layers: int | None = None, window: int | None = None) -> di
         raise FormatError(f"unknown shape '{name}' (known: {', '.join(sorted(SHAPES))})")
     raw = copy.deepcopy(SHAPES[name])
     if isinstance(raw.get("layers"), list):
-        if layers is not None:
-            raw["layers"] = [copy.deepcopy(raw["layers"][0]) for _ in range(layers)]
+        if layers is not None:                 # the pattern of layer kinds goes on (a shape may alternate two)
+            raw["layers"] = [copy.deepcopy(raw["layers"][i % len(raw["layers"])]) for i in range(layers)]
         if window is not None:
             for layer in raw["layers"]:
-                layer["mixer"]["mask"]["size"] = window
+                for mixer in (layer["mixer"], layer["mixer"].get("left")):
+                    if isinstance(mixer, dict) and "mask" in mixer:
+                        mixer["mask"]["size"] = window
     elif layers is not None:
         raw["num_hidden_layers"] = layers
     return raw
