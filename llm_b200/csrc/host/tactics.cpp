@@ -152,6 +152,12 @@ std::string sigmoid_tiles_guard(const Shape& s) {
     return "";
 }
 
+std::string sigmoid_decode_guard(const Shape& s) {
+    if (!s.decode) return "serves steps in which every sequence brings one token";
+    if (s.n_heads > 32) return std::to_string(s.n_heads) + " heads exceed the 32 rows of its tiles";
+    return sigmoid_tiles_guard(s);
+}
+
 const std::vector<Row>& table(int family) {
     static const std::vector<Row> linear = {
         {"gemm_tc", 30, tc_guard,
@@ -199,6 +205,10 @@ const std::vector<Row>& table(int family) {
          "up to 256, any group, window and kept first tokens; the only variant of the 32-bit path"},
     };
     static const std::vector<Row> sigmoid_attention = {
+        {"sigmoid_attention_decode", 20, sigmoid_decode_guard,
+         "one token a sequence: a block serves a slice of a sequence's pages for ALL heads (the heads are the rows of "
+         "the mma.sync tiles, the mixed queries of all heads lie in shared memory), so the window's keys and values "
+         "are read once; key and value tiles of all kv heads through a ring of four buffers; slices add in a fixed order"},
         {"sigmoid_attention_tiles", 10, sigmoid_tiles_guard,
          "tiles of 64 queries of one head on mma.sync over the pages the tile's windows reach; the mix over the heads "
          "is done on the queries (a mixed query of kv heads x head size elements in shared memory), the key tiles of "

@@ -395,5 +395,272 @@ LLMB_EXPORT int llmb_sigmoid_attention_tiles(const void* q, int q_stride, const 
     return fail(LLMB_ERR_ARGUMENT, "sigmoid_attention_tiles: head size %d with value size %d is not built", dim, vdim);
 }
 
+// ----------------------------------------------------------------------------- one token a sequence
+
+// sigmoid_attention_decode: a step in which every sequence brings one token is bound by reading the keys and
+// values of the window once. A block serves one (slice of the pages, sequence) for ALL heads: the heads are the
+// rows of the tensor-core tiles (16 * MT of them), the mixed queries of all heads lie in shared memory, and per
+// page the G key tiles and the G value tiles stream through a ring of four buffers. Each warp takes 16 of a
+// page's 64 keys; the weights of a head go into the second product only with the value tile of the head's own
+// group (the other rows of the operand are zero). Nothing is normalised, so the slices' results simply add: the
+// four warps are added in a fixed order, and with more than one slice a second kernel adds the slices in order.
+constexpr int DECODE_STAGES = 4;
+
+template <int D, int DV, int MT>
+__global__ void __launch_bounds__(WARPS * 32)
+sigmoid_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
+                                const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
+                                int table_stride, int ring_pages, const int* __restrict__ seq_lens,
+                                __nv_bfloat16* __restrict__ out, int out_stride, float* __restrict__ partial,
+                                int n_heads, int n_kv_heads, float scale, int window, const float* __restrict__ talk,
+                                const float* __restrict__ head_bias, float out_scale) {
+    constexpr int LDS = (D > DV ? D : DV) + PAD;
+    constexpr int TILE_ELEMS = LLMB_PAGE * LDS;
+    constexpr int ROWS = 16 * MT;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    griddep_launch();
+    griddep_wait();
+    int split = blockIdx.x, n_splits = gridDim.x, seq = blockIdx.y;
+    int group = n_heads / n_kv_heads;
+    int g_count = n_kv_heads;
+    int ldq = g_count * D + PAD;
+    __nv_bfloat16* mixed = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [ROWS][ldq]
+    __nv_bfloat16* ring = mixed + (size_t)ROWS * ldq;                       // [DECODE_STAGES][64][LDS]
+    int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gl = lane >> 2, t = lane & 3;
+    const int* pages = block_table + (size_t)seq * table_stride;
+    int len = seq_lens[seq];
+    int oldest = window > 0 ? max(len - window, 0) : 0;          // the query stands at len - 1
+    int first_page = oldest / LLMB_PAGE, n_pages = (len + LLMB_PAGE - 1) / LLMB_PAGE;
+    int per_split = (n_pages - first_page + n_splits - 1) / n_splits;
+    int page_begin = min(first_page + split * per_split, n_pages), page_end = min(page_begin + per_split, n_pages);
+    int units_per_page = 2 * g_count;
+    int n_units = (page_end - page_begin) * units_per_page;
+
+    auto load_unit = [&](int n) {
+        int p = page_begin + n / units_per_page, i = n % units_per_page;
+        size_t page = (size_t)pages[p % ring_pages];
+        __nv_bfloat16* to = ring + (size_t)(n % DECODE_STAGES) * TILE_ELEMS;
+        if (i < g_count) {
+            const __nv_bfloat16* from = k_cache + ((page * n_kv_heads + i) * LLMB_PAGE) * D;
+            for (int c = tid; c < LLMB_PAGE * (D / 8); c += WARPS * 32) {
+                int row = c / (D / 8), col = (c % (D / 8)) * 8;
+                cp_async16(to + row * LDS + col, from + (size_t)row * D + col);
+            }
+        } else {
+            const __nv_bfloat16* from = v_cache + ((page * n_kv_heads + (i - g_count)) * LLMB_PAGE) * DV;
+            for (int c = tid; c < LLMB_PAGE * (DV / 8); c += WARPS * 32) {
+                int row = c / (DV / 8), col = (c % (DV / 8)) * 8;
+                cp_async16(to + row * LDS + col, from + (size_t)row * DV + col);
+            }
+        }
+    };
+#pragma unroll
+    for (int n = 0; n < DECODE_STAGES - 1; ++n) {
+        if (n < n_units) load_unit(n);
+        cp_async_commit();
+    }
+    // the mixed queries of all heads: row a, key head g: sum over the heads b of group g of talk[a, b] * q_b
+    {
+        const __nv_bfloat16* q_row = q + (size_t)seq * q_stride;
+        int pairs = g_count * D / 2;
+        for (int idx = tid; idx < ROWS * pairs; idx += WARPS * 32) {
+            int a = idx / pairs, c = (idx % pairs) * 2;
+            int gi = c / D, d = c % D;
+            float lo = 0.f, hi = 0.f;
+            if (a < n_heads) {
+                for (int b = 0; b < group; ++b) {
+                    int other = gi * group + b;
+                    float w = talk ? talk[(size_t)a * n_heads + other] : (other == a ? 1.f : 0.f);
+                    lo = fmaf(w, to_float(q_row[(size_t)other * D + d]), lo);
+                    hi = fmaf(w, to_float(q_row[(size_t)other * D + d + 1]), hi);
+                }
+            }
+            *reinterpret_cast<__nv_bfloat162*>(mixed + (size_t)a * ldq + c) = __floats2bfloat162_rn(lo, hi);
+        }
+    }
+    float slope = -scale * 1.4426950408889634f;
+    float offset0[MT], offset1[MT];                  // -bias log2 e of this lane's two rows of every row tile
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+        int h0 = mt * 16 + gl, h1 = h0 + 8;
+        offset0[mt] = (head_bias && h0 < n_heads) ? -head_bias[h0] * 1.4426950408889634f : 0.f;
+        offset1[mt] = (head_bias && h1 < n_heads) ? -head_bias[h1] * 1.4426950408889634f : 0.f;
+    }
+
+    float acc[MT][DV / 8][4];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int n = 0; n < DV / 8; ++n)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[mt][n][e] = 0.f;
+    float s[MT][2][4];
+    uint32_t pa[MT][4];
+
+    for (int n = 0; n < n_units; ++n) {
+        cp_async_wait<DECODE_STAGES - 2>();
+        __syncthreads();                    // unit n landed (and, at n = 0, the mixed queries); all are done with unit n - 1
+        if (n + DECODE_STAGES - 1 < n_units) load_unit(n + DECODE_STAGES - 1);
+        cp_async_commit();
+        int p = page_begin + n / units_per_page, i = n % units_per_page;
+        int key_base = warp * 16;
+        int first_key = p * LLMB_PAGE + key_base;
+        if (first_key >= len || first_key + 16 <= oldest) continue;      // none of this warp's 16 keys is seen
+        const __nv_bfloat16* tile_s = ring + (size_t)(n % DECODE_STAGES) * TILE_ELEMS;
+        if (i == 0) {
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+                for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[mt][nb][e] = 0.f;
+        }
+        if (i < g_count) {
+#pragma unroll
+            for (int kstep = 0; kstep < D / 16; ++kstep) {
+                uint32_t b[4];
+                ldmatrix_x4(b, tile_s + (key_base + (lane >> 4) * 8 + (lane & 7)) * LDS + kstep * 16 + ((lane >> 3) & 1) * 8);
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    uint32_t a[4];
+                    ldmatrix_x4(a, mixed + (size_t)(mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldq + i * D + kstep * 16 + (lane >> 4) * 8);
+                    mma_bf16(s[mt][0], a[0], a[1], a[2], a[3], b[0], b[1]);
+                    mma_bf16(s[mt][1], a[0], a[1], a[2], a[3], b[2], b[3]);
+                }
+            }
+            if (i == g_count - 1) {                 // the scores are complete: the weights, as the second product's operand
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+                    for (int nb = 0; nb < 2; ++nb)
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            int key = first_key + nb * 8 + 2 * t + e;
+                            bool seen = key < len && key >= oldest;
+                            float w0 = __frcp_rn(1.0f + fast_exp2(fmaf(s[mt][nb][e], slope, offset0[mt])));
+                            float w1 = __frcp_rn(1.0f + fast_exp2(fmaf(s[mt][nb][2 + e], slope, offset1[mt])));
+                            s[mt][nb][e] = seen ? w0 : 0.f;
+                            s[mt][nb][2 + e] = seen ? w1 : 0.f;
+                        }
+                    pa[mt][0] = pack_bf16(s[mt][0][0], s[mt][0][1]);
+                    pa[mt][1] = pack_bf16(s[mt][0][2], s[mt][0][3]);
+                    pa[mt][2] = pack_bf16(s[mt][1][0], s[mt][1][1]);
+                    pa[mt][3] = pack_bf16(s[mt][1][2], s[mt][1][3]);
+                }
+            }
+            continue;
+        }
+        int gv = i - g_count;                       // the value tile of key/value head gv: only its group's rows
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+            if (gv < (mt * 16) / group || gv > (mt * 16 + 15) / group) continue;       // no head of this row tile
+            bool mine0 = (mt * 16 + gl) / group == gv, mine1 = (mt * 16 + gl + 8) / group == gv;
+            uint32_t a0 = mine0 ? pa[mt][0] : 0u, a1 = mine1 ? pa[mt][1] : 0u;
+            uint32_t a2 = mine0 ? pa[mt][2] : 0u, a3 = mine1 ? pa[mt][3] : 0u;
+#pragma unroll
+            for (int n2 = 0; n2 < DV / 8; n2 += 2) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, tile_s + (key_base + ((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + (n2 + (lane >> 4)) * 8);
+                mma_bf16(acc[mt][n2], a0, a1, a2, a3, b[0], b[1]);
+                mma_bf16(acc[mt][n2 + 1], a0, a1, a2, a3, b[2], b[3]);
+            }
+        }
+    }
+    cp_async_wait<0>();
+    __syncthreads();                                // the buffers are free: the four warps' sums meet in them
+    float* merge = reinterpret_cast<float*>(smem_raw);          // [WARPS][ROWS][DV]
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int n = 0; n < DV / 8; ++n) {
+            float* to = merge + ((size_t)warp * ROWS + mt * 16 + gl) * DV + n * 8 + 2 * t;
+            to[0] = acc[mt][n][0];
+            to[1] = acc[mt][n][1];
+            to[8 * DV] = acc[mt][n][2];
+            to[8 * DV + 1] = acc[mt][n][3];
+        }
+    __syncthreads();
+    for (int idx = tid; idx < n_heads * DV; idx += WARPS * 32) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) v += merge[(size_t)w * ROWS * DV + idx];
+        if (n_splits == 1) out[(size_t)seq * out_stride + idx] = __float2bfloat16_rn(v * out_scale);
+        else partial[((size_t)seq * n_splits + split) * n_heads * DV + idx] = v;
+    }
+}
+
+__global__ void sigmoid_attention_add_slices_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out,
+                                                    int out_stride, int width, int n_splits, float out_scale) {
+    griddep_launch();
+    griddep_wait();
+    int seq = blockIdx.y;
+    int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= width) return;
+    float v = 0.f;
+    for (int s = 0; s < n_splits; ++s) v += partial[((size_t)seq * n_splits + s) * width + idx];
+    out[(size_t)seq * out_stride + idx] = __float2bfloat16_rn(v * out_scale);
+}
+
+template <int D, int DV, int MT>
+static int launch_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache, const int* block_table,
+                         int table_stride, int ring_pages, const int* seq_lens, void* out, int out_stride, float* scratch,
+                         int n_seqs, int n_heads, int n_kv_heads, float scale, int window, const float* talk,
+                         const float* head_bias, float out_scale, int n_splits, cudaStream_t stream) {
+    constexpr int LDS = (D > DV ? D : DV) + PAD;
+    constexpr int ROWS = 16 * MT;
+    size_t stream_bytes = sizeof(__nv_bfloat16) * ((size_t)ROWS * (n_kv_heads * D + PAD) + (size_t)DECODE_STAGES * LLMB_PAGE * LDS);
+    size_t merge_bytes = sizeof(float) * WARPS * ROWS * DV;
+    size_t smem = stream_bytes > merge_bytes ? stream_bytes : merge_bytes;
+    LLMB_REQUIRE(smem <= 220 * 1024, "sigmoid_attention_decode: %d key heads of %d do not fit in shared memory", n_kv_heads, D);
+    static size_t configured = 0;
+    if (smem > configured) {
+        LLMB_CUDA(cudaFuncSetAttribute(sigmoid_attention_decode_kernel<D, DV, MT>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    LLMB_CUDA(llmb::launch(sigmoid_attention_decode_kernel<D, DV, MT>, dim3(n_splits, n_seqs), dim3(WARPS * 32), smem, stream,
+                           true, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
+                           (const __nv_bfloat16*)v_cache, block_table, table_stride, ring_pages, seq_lens,
+                           (__nv_bfloat16*)out, out_stride, scratch, n_heads, n_kv_heads, scale, window, talk, head_bias,
+                           out_scale));
+    if (n_splits > 1) {
+        int width = n_heads * DV;
+        LLMB_CUDA(llmb::launch(sigmoid_attention_add_slices_kernel, dim3(ceil_div(width, 256), n_seqs), dim3(256), 0, stream,
+                               true, (const float*)scratch, (__nv_bfloat16*)out, out_stride, width, n_splits, out_scale));
+    }
+    return check_launch("sigmoid_attention_decode");
+}
+
+// One query a sequence (row b of q is sequence b's, at position seq_lens[b] - 1). scratch: n_seqs * n_splits *
+// n_heads * vdim floats where n_splits > 1. Up to 32 heads.
+LLMB_EXPORT int llmb_sigmoid_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
+                                              const int* block_table, int table_stride, int ring_pages,
+                                              const int* seq_lens, void* out, int out_stride, float* scratch,
+                                              long long scratch_floats, int n_seqs, int n_heads, int n_kv_heads, int dim,
+                                              int vdim, float scale, int window, const float* talk,
+                                              const float* head_bias, float out_scale, int n_splits, cudaStream_t stream) {
+    if (n_seqs == 0) return LLMB_OK;
+    LLMB_REQUIRE(n_heads > 0 && n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_heads <= 32,
+                 "sigmoid_attention_decode: %d heads over %d kv heads (up to 32 heads)", n_heads, n_kv_heads);
+    LLMB_REQUIRE(n_seqs <= 65535 && n_splits >= 1 && n_splits <= 65535 && ring_pages > 0 && window >= 0,
+                 "sigmoid_attention_decode: bad sizes");
+    LLMB_REQUIRE(n_splits == 1 || (scratch && scratch_floats >= (long long)n_seqs * n_splits * n_heads * vdim),
+                 "sigmoid_attention_decode: scratch too small");
+#define X(DK, DVAL)                                                                                                   \
+    if (dim == DK && vdim == DVAL) {                                                                                  \
+        if (n_heads <= 16)                                                                                            \
+            return launch_decode<DK, DVAL, 1>(q, q_stride, k_cache, v_cache, block_table, table_stride, ring_pages,  \
+                                              seq_lens, out, out_stride, scratch, n_seqs, n_heads, n_kv_heads, scale, \
+                                              window, talk, head_bias, out_scale, n_splits, stream);                  \
+        return launch_decode<DK, DVAL, 2>(q, q_stride, k_cache, v_cache, block_table, table_stride, ring_pages,      \
+                                          seq_lens, out, out_stride, scratch, n_seqs, n_heads, n_kv_heads, scale,     \
+                                          window, talk, head_bias, out_scale, n_splits, stream);                      \
+    }
+    LLMB_SIGMOID_SHAPES(X)
+#undef X
+    return fail(LLMB_ERR_ARGUMENT, "sigmoid_attention_decode: head size %d with value size %d is not built", dim, vdim);
+}
+
 LLMB_PACKED(llmb_sigmoid_attention_generic)
 LLMB_PACKED(llmb_sigmoid_attention_tiles)
+LLMB_PACKED(llmb_sigmoid_attention_decode)

@@ -898,8 +898,17 @@ def attention_replay_key(step, n_kv_heads: int):
     return (False, max(step.new_counts))
 
 
+def sigmoid_decode_splits(n_seqs: int, max_len: int, window: int) -> int:
+    """Slices of the decode kernel of the sigmoid attention (a block serves all heads of a sequence):
+    `decode_splits` for the keys a query sees at most."""
+    seen = min(max_len, window + PAGE) if window > 0 else max_len
+    return decode_splits(n_seqs, 1, seen)
+
+
 def sigmoid_attention_replay_key(step, spec):
-    return (bool(step.decode), max(step.new_counts))
+    if step.decode:
+        return (True, sigmoid_decode_splits(step.n_seqs, step.max_len, spec.window))
+    return (False, max(step.new_counts))
 
 
 def sigmoid_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads, n_kv_heads, dim, vdim,
@@ -926,6 +935,23 @@ def sigmoid_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok
     variant = tactics.choose_sigmoid_attention(
         decode, q.dtype, n_heads, n_kv_heads, dim, vdim, window, cu_seqlens is not None and seq_lens is not None,
         q.stride(0) % 2 == 0 and out.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0 and out.data_ptr() % 4 == 0)
+    if variant == "sigmoid_attention_decode":
+        splits = sigmoid_decode_splits(n, max_len, window)
+        need = n * splits * n_heads * vdim if splits > 1 else 0
+        scratch = _attention_scratch.get(q.device)
+        if scratch is None or scratch.numel() < need:
+            if scratch is not None:
+                global _scratch_generation
+                _retired.append(scratch)
+                _scratch_generation += 1
+            scratch = torch.empty(max(need, 1 << 23), dtype=torch.float32, device=q.device)
+            _attention_scratch[q.device] = scratch
+        _call("sigmoid_attention", "llmb_sigmoid_attention_decode", _ptr(q), _c_int(q.stride(0)), _ptr(k_cache),
+              _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(seq_lens),
+              _ptr(out), _c_int(out.stride(0)), _ptr(scratch), ctypes.c_longlong(scratch.numel()), _c_int(n),
+              _c_int(n_heads), _c_int(n_kv_heads), _c_int(dim), _c_int(vdim), _c_float(scale), _c_int(window),
+              _ptr(talk), _ptr(head_bias), _c_float(out_scale), _c_int(splits), _stream(), kernels=2 if splits > 1 else 1)
+        return out
     if variant == "sigmoid_attention_tiles":
         _call("sigmoid_attention", "llmb_sigmoid_attention_tiles", _ptr(q), _c_int(q.stride(0)), _ptr(k_cache),
               _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(cu_seqlens),
@@ -1094,6 +1120,6 @@ def required_libraries() -> list:
 
 __all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "random_normal_", "begin_recording", "end_recording", "RecordedPass", "scratch_generation", "Emit", "FoldedNorm", "RopeWrite", "cast_sumsq", "SUMSQ_LD", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
            "softcap_", "add_rows_", "conv_rope_cache_write", "diff_attention", "tanh_norm", "norm_rope_cache_write",
-           "sigmoid_attention", "gated_recurrence", "attention_replay_key", "sigmoid_attention_replay_key",
+           "sigmoid_attention", "gated_recurrence", "attention_replay_key", "sigmoid_attention_replay_key", "sigmoid_decode_splits",
            "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "check_device_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

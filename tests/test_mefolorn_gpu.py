@@ -154,7 +154,7 @@ def _attention(fn, batch, heads, groups, dim, dtype, window, sinks, gated, share
 
 class only_generic:
     """Inside: the tensor-core attention kernels are switched off, so the generic ones run in bfloat16 too."""
-    NAMES = ("attention_prefill", "sigmoid_attention_tiles")
+    NAMES = ("attention_prefill", "sigmoid_attention_tiles", "sigmoid_attention_decode")
 
     def __init__(self, on=True):
         self.on = on
@@ -263,14 +263,15 @@ def _sigmoid(fn, batch, heads, groups, dim, vdim, dtype, window, talk, bias, see
     # heads, kv heads, head size, value size, window, mixed, bias
     (4, 2, 6, 10, 9, True, True), (2, 2, 8, 5, 33, True, True), (4, 2, 64, 32, 40, True, True),
     (4, 1, 32, 64, 100, True, True), (2, 1, 16, 24, 0, True, True), (3, 1, 20, 20, 7, False, True),
-    (4, 4, 64, 64, 64, True, False), (8, 2, 128, 128, 200, True, True), (16, 4, 96, 96, 65, True, True)])
+    (4, 4, 64, 64, 64, True, False), (8, 2, 128, 128, 200, True, True), (16, 4, 96, 96, 65, True, True),
+    (32, 8, 64, 64, 100, True, True), (32, 4, 32, 32, 0, False, True), (24, 8, 64, 128, 70, True, True)])
 @pytest.mark.parametrize("generic", [False, True])
 def test_sigmoid_attention(dtype, case, generic):
     ops = _ops()
     heads, groups, dim, vdim, window, talk, bias = case
     if generic and dtype == torch.float32:
         pytest.skip("the 32-bit path is the generic kernel already")
-    for lengths, new in BATCHES + [([700, 64, 129], [700, 3, 129])]:
+    for lengths, new in BATCHES + [([700, 64, 129], [700, 3, 129]), ([1500, 1, 64, 65, 700], [1] * 5), ([2200], [1])]:
         batch = Batch(lengths, new, seed=7 + len(lengths))
         with only_generic(generic):
             got = _sigmoid(ops.sigmoid_attention, batch, heads, groups, dim, vdim, dtype, window, talk, bias)
