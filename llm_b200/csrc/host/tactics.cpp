@@ -68,8 +68,6 @@ bool mma_head_dim(int d) { return d == 32 || d == 64 || d == 96 || d == 128; }
 std::string decode_guard(const Shape& s) {
     if (!s.decode) return "serves steps in which every sequence brings one token";
     if (!s.bf16) return "bfloat16 caches only";
-    if (s.window) return "no window";
-    if (s.n_heads / s.n_kv_heads > 8) return "group of " + std::to_string(s.n_heads / s.n_kv_heads) + " query heads exceeds 8";
     if (!mma_head_dim(s.head_dim)) return "head_dim " + std::to_string(s.head_dim) + " (served: 32, 64, 96, 128)";
     return "";
 }
@@ -175,7 +173,8 @@ const std::vector<Row>& table(int family) {
     static const std::vector<Row> attention = {
         {"attention_decode", 20, decode_guard,
          "split-KV decode attention: pages through shared memory with cp.async (a ring sized by the head size), "
-         "the query heads of a group as rows of mma.sync tiles, partials merged by a second kernel. Measured: "
+         "the query heads of a group as rows of mma.sync tiles (groups above 8 as several blocks), partials merged by a "
+         "second kernel; windows, a sink term, a gate per head, a value cache that is the key cache. Measured: "
          "45.2 us for 8 sequences of 8,192 keys with 8 kv heads of 128 (5.94 TB/s)"},
         {"attention_prefill_tc", 15, prefill_tc_guard,
          "flash attention with both products on tcgen05 (accumulators in tensor memory, K and V pages by TMA), "

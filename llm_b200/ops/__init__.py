@@ -800,6 +800,14 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
     return splits
 
 
+def attention_decode_splits(n_seqs: int, n_heads: int, n_kv_heads: int, max_len: int, window: int = 0) -> int:
+    """Slices of the decode attention kernel: `decode_splits` for its blocks a sequence (a group of more
+    than 8 query heads is several blocks over one key/value head) and the keys a query sees at most."""
+    chunks = (n_heads // max(n_kv_heads, 1) + 7) // 8
+    seen = min(max_len, window + PAGE) if window > 0 else max_len
+    return decode_splits(n_seqs, n_kv_heads * chunks, seen)
+
+
 def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, n_heads,
               n_kv_heads, head_dim, scale, window=0, out=None, decode=False, seq_lens=None,
               max_len=0, cu_seqlens=None, max_new=0, seq_order=None, sinks=None, gate=None, out_scale=1.0):
@@ -839,6 +847,8 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
                 and cu_seqlens is not None and seq_lens is not None and qkv.stride(0) % 2 == 0 and out.stride(0) % 2 == 0 \
                 and qkv.data_ptr() % 4 == 0 and out.data_ptr() % 4 == 0:
             variant = "attention_prefill"
+    if variant == "attention_decode" and (qkv.stride(0) % 2 or qkv.data_ptr() % 4):
+        variant = "attention_generic"
     if variant == "attention_prefill_tc":
         _call("attention_prefill_tc", "llmb_attention_prefill_tc", _ptr(qkv), _c_int(qkv.stride(0)),
               _c_int(n), _ptr(k_cache), _ptr(v_cache), _c_int(k_cache.shape[0]), _ptr(block_table),
@@ -854,7 +864,7 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
               _c_int(head_dim), _c_float(scale), _c_int(window), _ptr(sinks), _ptr(gate),
               _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _stream())
     elif variant == "attention_decode":
-        splits = decode_splits(n, n_kv_heads, max_len)
+        splits = attention_decode_splits(n, n_heads, n_kv_heads, max_len, window)
         lib = load_library("attention_decode")
         lib.llmb_attention_decode_scratch_floats.restype = ctypes.c_longlong
         need = lib.llmb_attention_decode_scratch_floats(_c_int(n), _c_int(n_heads), _c_int(head_dim),
@@ -872,7 +882,8 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
               _c_int(ring_pages), _ptr(seq_lens), _ptr(seq_order), _ptr(out), _c_int(out.stride(0)),
               _ptr(scratch),
               ctypes.c_longlong(scratch.numel()), _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
-              _c_int(head_dim), _c_float(scale), _c_int(window), _c_int(splits), _stream(),
+              _c_int(head_dim), _c_float(scale), _c_int(window), _ptr(sinks), _ptr(gate),
+              _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _c_int(splits), _stream(),
               kernels=2 if splits > 1 else 1)
     elif variant == "attention_generic":
         _call("attention_generic", "llmb_attention_generic", _ptr(qkv), _c_int(qkv.stride(0)),
@@ -887,14 +898,14 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
 
 
 # the attention kernels that take a sink, a gate and a scale of the result
-_ATTENTION_WITH_EXTRAS = ("attention_generic", "attention_prefill")
+_ATTENTION_WITH_EXTRAS = ("attention_generic", "attention_prefill", "attention_decode")
 
 
-def attention_replay_key(step, n_kv_heads: int):
+def attention_replay_key(step, n_heads: int, n_kv_heads: int, window: int = 0):
     """What the launches of `attention` depend on beyond the token and sequence counts
     (Part.replay_key): the most new tokens of a sequence (prefill grids), the slices (decode)."""
     if step.decode:
-        return (True, decode_splits(step.n_seqs, n_kv_heads, step.max_len))
+        return (True, attention_decode_splits(step.n_seqs, n_heads, n_kv_heads, step.max_len, window))
     return (False, max(step.new_counts))
 
 
@@ -1120,6 +1131,6 @@ def required_libraries() -> list:
 
 __all__ = ["PAGE", "GLU_BLOCK", "glu_fusable", "embed", "scale_", "random_normal_", "begin_recording", "end_recording", "RecordedPass", "scratch_generation", "Emit", "FoldedNorm", "RopeWrite", "cast_sumsq", "SUMSQ_LD", "rmsnorm", "swiglu", "rope_cache_write", "linear", "attention",
            "softcap_", "add_rows_", "conv_rope_cache_write", "diff_attention", "tanh_norm", "norm_rope_cache_write",
-           "sigmoid_attention", "gated_recurrence", "attention_replay_key", "sigmoid_attention_replay_key", "sigmoid_decode_splits",
+           "sigmoid_attention", "gated_recurrence", "attention_replay_key", "attention_decode_splits", "sigmoid_attention_replay_key", "sigmoid_decode_splits",
            "argmax_rows", "sample_rows", "launch_count", "count_launches", "tensor_core_status", "check_device_status", "ensure_built", "load_library", "all_sources",
            "required_libraries", "tactics"]

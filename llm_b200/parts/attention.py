@@ -94,9 +94,7 @@ class AttentionMixer(Mixer):
         """The attention kernels size their grids by the most new tokens of a sequence (prefill) or
         by the slices of the longest sequence (decode); positions, lengths and pages come from
         device arrays."""
-        if step.decode:
-            return (True, ops.decode_splits(step.n_seqs, self.spec.n_kv_heads, step.max_len))
-        return (False, max(step.new_counts))
+        return ops.attention_replay_key(step, self.spec.n_heads, self.spec.n_kv_heads, self.spec.window)
 
     def forward(self, h, ctx, entry, cache_entry, residual, emit=None):
         s = self.spec

@@ -89,7 +89,7 @@ class LatentAttentionMixer(ProjectedMixer):
                 BufferRequest("queries", (n_tokens, self.out_width), dtype, 1, 2)]
 
     def mix_replay_key(self, step):
-        return ops.attention_replay_key(step, 1)
+        return ops.attention_replay_key(step, self.spec.n_heads, 1, self.spec.window)
 
     def mix_shapes(self, dtype, token_counts):
         s, out = self.spec, []

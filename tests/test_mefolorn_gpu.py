@@ -154,7 +154,7 @@ def _attention(fn, batch, heads, groups, dim, dtype, window, sinks, gated, share
 
 class only_generic:
     """Inside: the tensor-core attention kernels are switched off, so the generic ones run in bfloat16 too."""
-    NAMES = ("attention_prefill", "sigmoid_attention_tiles", "sigmoid_attention_decode")
+    NAMES = ("attention_prefill", "attention_decode", "sigmoid_attention_tiles", "sigmoid_attention_decode")
 
     def __init__(self, on=True):
         self.on = on
@@ -179,13 +179,14 @@ class only_generic:
     (4, 1, 64, 70, True, True, True), (3, 1, 9, 5, True, True, True), (8, 1, 32, 130, True, False, True),
     (2, 1, 34, 21, False, True, True), (4, 2, 16, 0, True, True, False), (2, 1, 320, 40, True, True, True),
     (16, 1, 128, 64, True, True, True), (4, 1, 96, 1, True, True, True), (4, 2, 64, 0, False, False, False),
-    (2, 1, 128, 300, True, True, True), (6, 3, 32, 63, False, True, False)])
+    (2, 1, 128, 300, True, True, True), (6, 3, 32, 63, False, True, False), (32, 1, 128, 1000, True, True, True),
+    (20, 2, 64, 0, True, False, False)])
 def test_attention_with_sink_gate_and_shared_values(dtype, case, generic):
     ops = _ops()
     heads, groups, dim, window, sinks, gated, shared = case
     if generic and dtype == torch.float32:
         pytest.skip("the 32-bit path is the generic kernel already")
-    for lengths, new in BATCHES + [([700, 64, 129], [700, 3, 129])]:
+    for lengths, new in BATCHES + [([700, 64, 129], [700, 3, 129]), ([1500, 1, 64, 65, 700], [1] * 5), ([2200], [1])]:
         batch = Batch(lengths, new, seed=3 + len(lengths))
         with only_generic(generic):
             got = _attention(ops.attention, batch, heads, groups, dim, dtype, window, sinks, gated, shared, 0.8)

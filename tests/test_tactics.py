@@ -74,13 +74,16 @@ def test_family_shapes_get_the_fast_kernels(name):
 def test_refusals_name_the_assumption_that_fails():
     text = tactics.explain("attention", decode=True, dtype=BF16, n_heads=32, n_kv_heads=2, head_dim=128,
                            window=0, packed=True)
-    assert text.startswith("attention: attention_prefill_tc") and "group of 16 query heads exceeds 8" in text
+    assert text.startswith("attention: attention_decode")               # a group of 16 heads: two blocks a key/value head
+    text = tactics.explain("attention", decode=False, dtype=BF16, n_heads=32, n_kv_heads=2, head_dim=128,
+                           window=100, packed=True)
+    assert text.startswith("attention: attention_prefill") and "no window" in text        # the tcgen05 kernel has none
     text = tactics.explain("attention", decode=False, dtype=BF16, n_heads=4, n_kv_heads=4, head_dim=80,
                            window=0, packed=True)
     assert text.startswith("attention: attention_generic") and "head_dim 80" in text
     text = tactics.explain("attention", decode=True, dtype=BF16, n_heads=4, n_kv_heads=2, head_dim=64,
                            window=100, packed=True)
-    assert text.startswith("attention: attention_prefill") and "no window" in text        # the flash kernel takes windows
+    assert text.startswith("attention: attention_decode")               # the decode kernel takes windows
     text = tactics.explain("linear", m=2048, n=4096, k=4100, in_dtype=BF16, out_dtype=BF16, lda=4100)
     assert text.startswith("linear: gemm_simt") and "multiple of 8" in text and "exceed 64" in text
 
