@@ -989,8 +989,8 @@ def gated_recurrence(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_b
     [blocks, C / blocks, C / blocks], rows = outputs). a = exp(rate * r) (rate float32 [C], negative),
     S <- a S + sqrt(1 - a^2) i u, out[t] = out_scale * S * gelu(y[t]) (tanh form). `state` float32
     [slots, taps, C]: rows 0 .. taps - 2 the convolution's last inputs (oldest first), the last row
-    S; it is read at the slot of each sequence and brought up to date. `work` float32 [2, T, C]:
-    a and the driving term of every token, between the two kernels. Everything but the rounding of
+    S; it is read at the slot of each sequence and brought up to date. `work` float32 [3, T, C]:
+    u, a and the driving term of every token, between the three kernels. Everything but the rounding of
     `out` is 32-bit."""
     _require_cuda(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_bias, rate, state, tok_seq, cu_seqlens,
                   slot_ids, out, work)
@@ -1007,13 +1007,13 @@ def gated_recurrence(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_b
             raise KernelError(f"gated_recurrence: a parameter is {tuple(t.shape)} {t.dtype}, not contiguous float32 {shape}")
     if state.dtype != torch.float32 or tuple(state.shape[1:]) != (taps, channels) or not state.is_contiguous():
         raise KernelError(f"gated_recurrence: the state must be contiguous float32 [slots, {taps}, {channels}]")
-    if work.dtype != torch.float32 or tuple(work.shape) != (2, n, channels) or not work.is_contiguous():
-        raise KernelError(f"gated_recurrence: work must be contiguous float32 [2, {n}, {channels}]")
+    if work.dtype != torch.float32 or tuple(work.shape) != (3, n, channels) or not work.is_contiguous():
+        raise KernelError(f"gated_recurrence: work must be contiguous float32 [3, {n}, {channels}]")
     _call("gated_recurrence", "llmb_gated_recurrence", _ptr(y), _c_int(y.stride(0)), _ptr(x), _c_int(x.stride(0)),
           _c_int(_code(y.dtype)), _ptr(conv_w), _ptr(conv_b), _c_int(taps), _ptr(gate_a), _ptr(gate_a_bias),
           _ptr(gate_i), _ptr(gate_i_bias), _c_int(blocks), _ptr(rate), _ptr(state), _ptr(tok_seq), _ptr(cu_seqlens),
           _ptr(slot_ids), _ptr(out), _c_int(out.stride(0)), _c_float(out_scale), _ptr(work), _c_int(n),
-          _c_int(channels), _c_int(cu_seqlens.numel() - 1), _stream(), kernels=2)
+          _c_int(channels), _c_int(cu_seqlens.numel() - 1), _stream(), kernels=3)
     return out
 
 

@@ -77,14 +77,14 @@ class GatedRecurrenceMixer(ProjectedMixer):
     def mix_scratch(self, n_tokens, dtype):
         from ..engine.workspace import BufferRequest
         # phase 0: both kernels (the scan reads what the gates wrote)
-        return [BufferRequest("decay_drive", (2, n_tokens, self.spec.width), torch.float32, 0, 0)]
+        return [BufferRequest("decay_drive", (3, n_tokens, self.spec.width), torch.float32, 0, 0)]
 
     def mix(self, proj, ctx, entry, cache_entry, out, scratch):
         s = self.spec
         n = proj.shape[0]
-        work = scratch("decay_drive", (2, n, s.width), torch.float32)
+        work = scratch("decay_drive", (3, n, s.width), torch.float32)
         if work is None:
-            work = torch.empty((2, n, s.width), dtype=torch.float32, device=proj.device)
+            work = torch.empty((3, n, s.width), dtype=torch.float32, device=proj.device)
         ops.gated_recurrence(proj[:, :s.width], proj[:, s.width:], self.conv, self.conv_bias, self.gate_a,
                              self.gate_a_bias, self.gate_i, self.gate_i_bias, self.rate, ctx.cache.state_view(entry),
                              ctx.tok_seq, ctx.cu_seqlens, ctx.slot_ids, out, s.out_scale, work)

@@ -339,7 +339,7 @@ def _recurrence_inputs(channels, blocks, taps, n_tokens, n_slots, dtype, seed):
 
 def _recurrence(fn, wide, params, state, batch, channels, dtype):
     out_wide = torch.zeros((batch.n_tokens, channels + 9), dtype=dtype, device=DEV)
-    work = torch.empty((2, batch.n_tokens, channels), device=DEV)
+    work = torch.empty((3, batch.n_tokens, channels), device=DEV)
     p = params
     fn(wide[:, 2:2 + channels], wide[:, 2 + channels:2 + 2 * channels], p["conv_w"], p["conv_b"], p["gate_a"], p["gate_a_bias"],
        p["gate_i"], p["gate_i_bias"], p["rate"], state, batch.tok_seq, batch.cu, batch.slots, out_wide[:, 4:4 + channels], 0.9, work)
@@ -351,7 +351,8 @@ def _recurrence(fn, wide, params, state, batch, channels, dtype):
 def test_gated_recurrence(dtype, case):
     ops = _ops()
     channels, blocks, taps = case
-    for lengths, new in BATCHES:
+    # (steps of more than 256 tokens scan in chunks: sequences that begin and end inside and across chunks)
+    for lengths, new in BATCHES + [([700, 64, 129, 5, 2], [700, 3, 129, 5, 1]), ([60, 900, 3, 131], [60, 320, 3, 131])]:
         batch = Batch(lengths, new, seed=1)
         wide, params, state = _recurrence_inputs(channels, blocks, taps, batch.n_tokens, len(lengths) + 2, dtype, seed=channels)
         states = [state.clone(), state.clone()]
