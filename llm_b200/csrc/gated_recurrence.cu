@@ -246,6 +246,25 @@ __device__ __forceinline__ void update_conv_rows(float* rows, int taps, int chan
     }
 }
 
+// A step in which every sequence brings one token: token b is sequence b's, nothing is walked.
+template <typename T>
+__global__ void __launch_bounds__(256)
+scan_single_kernel(const T* __restrict__ y, int y_stride, const T* __restrict__ x, int x_stride,
+                   const float* __restrict__ decay, const float* __restrict__ drive, float* __restrict__ state, int taps,
+                   int channels, const int* __restrict__ slot_ids, T* __restrict__ out, int out_stride, float out_scale) {
+    griddep_launch();
+    griddep_wait();
+    int c = blockIdx.x * 256 + threadIdx.x;
+    if (c >= channels) return;
+    int t = blockIdx.y;
+    float* rows = state + (size_t)slot_ids[t] * taps * channels + c;
+    float s = fmaf(decay[(size_t)t * channels + c], rows[(size_t)(taps - 1) * channels], drive[(size_t)t * channels + c]);
+    out[(size_t)t * out_stride + c] = from_float<T>(s * gelu_tanh(to_float(y[(size_t)t * y_stride + c])) * out_scale);
+    rows[(size_t)(taps - 1) * channels] = s;
+    for (int r = 0; r + 1 < taps - 1; ++r) rows[(size_t)r * channels] = rows[(size_t)(r + 1) * channels];
+    if (taps > 1) rows[(size_t)(taps - 2) * channels] = to_float(x[(size_t)t * x_stride + c]);
+}
+
 // Pass 1 of the chunked scan. A sequence's first token of the step becomes a token without a carry: its
 // driving term takes a * S(state) in, its a becomes 0 (both rewritten in place).
 __global__ void __launch_bounds__(SCAN_THREADS)
@@ -323,7 +342,7 @@ LLMB_EXPORT int llmb_gated_recurrence(const void* y, int y_stride, const void* x
                                       int blocks, const float* rate, float* state, const int* tok_seq,
                                       const int* cu_seqlens, const int* slot_ids, void* out, int out_stride,
                                       float out_scale, float* work, int n_tokens, int channels, int n_seqs,
-                                      cudaStream_t stream) {
+                                      int single_tokens, cudaStream_t stream) {
     if (n_tokens == 0) return LLMB_OK;
     LLMB_REQUIRE(taps >= 1 && taps <= MAX_TAPS, "gated_recurrence: %d taps (1 to %d are built)", taps, MAX_TAPS);
     LLMB_REQUIRE(channels > 0 && blocks > 0 && channels % blocks == 0 && n_seqs > 0,
@@ -344,7 +363,12 @@ LLMB_EXPORT int llmb_gated_recurrence(const void* y, int y_stride, const void* x
                                source, tok_seq, cu_seqlens, slot_ids, u));                                          \
         LLMB_CUDA(llmb::launch(gates, grid_gates, dim3(256), 0, stream, true, (const float*)u, channels, gate_a,    \
                                gate_a_bias, gate_i, gate_i_bias, part, rate, decay, drive, n_tokens));              \
-        if (n_tokens <= SCAN_SERIAL) {                                                                              \
+        if (n_tokens == n_seqs && single_tokens) {                                                                  \
+            LLMB_CUDA(llmb::launch(scan_single_kernel<T>, dim3(ceil_div(channels, 256), n_seqs), dim3(256), 0, stream, \
+                                   true, (const T*)y, y_stride, (const T*)x, x_stride, (const float*)decay,         \
+                                   (const float*)drive, state, taps, channels, slot_ids, (T*)out, out_stride,       \
+                                   out_scale));                                                                     \
+        } else if (n_tokens <= SCAN_SERIAL) {                                                                       \
             LLMB_CUDA(llmb::launch(scan_kernel<T>, grid_scan, dim3(SCAN_THREADS), 0, stream, true, (const T*)y,     \
                                    y_stride, (const T*)x, x_stride, (const float*)decay, (const float*)drive,       \
                                    state, taps, channels, cu_seqlens, slot_ids, (T*)out, out_stride, out_scale));   \

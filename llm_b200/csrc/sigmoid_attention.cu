@@ -22,14 +22,15 @@
 // is done on them: with G key/value heads, the mixed score of head a is
 //     sum over g of (sum over the heads b of group g of talk[a, b] q_b) . k_g,
 // one product of a "mixed query" of G * dim elements with the keys of all G heads at a position. A block
+// (eight warps: two share 16 query rows and take half of a page's keys each; their sums meet at the end)
 // forms its tile's mixed queries once (32-bit sums, rounded to bfloat16 as any query is) in shared memory;
 // per page it runs the G key tiles and then the value tile of its own group through a ring of three
 // buffers (cp.async, two units in flight), S accumulating over the key tiles in 32-bit; the weights
 // sigmoid(scale S + bias) are formed in 32-bit, masked at the diagonal and at the window's lower edge, and
 // become the A operand of the second product. Nothing is normalised, so there is no running maximum and no
 // rescaling. Without a matrix the mixed query is the head's own and G is 1. The price of mixing is G times
-// the score products of a plain attention; a step in which every sequence brings one token runs the same
-// kernel with one live row a tile.
+// the score products of a plain attention. Steps in which every sequence brings one token have a kernel of
+// their own (below); this one also serves them (one live row a tile) where that one does not.
 #include "common.cuh"
 #include "mma.cuh"
 
@@ -157,6 +158,7 @@ LLMB_EXPORT int llmb_sigmoid_attention_generic(const void* q, int q_stride, cons
 // ----------------------------------------------------------------------------- tiles on the tensor cores
 
 constexpr int BQ = WARPS * 16;               // queries per block
+constexpr int TILE_WARPS = 2 * WARPS;        // two warps share 16 query rows and halve a page's keys
 constexpr int STAGES = 3;
 constexpr int PAD = 8;
 
@@ -167,7 +169,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 template <int D, int DV>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(TILE_WARPS * 32)
 sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
                                const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                                int table_stride, int ring_pages, const int* __restrict__ cu_seqlens,
@@ -190,7 +192,8 @@ sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
     int ldq = g_count * D + PAD;
     __nv_bfloat16* mixed = reinterpret_cast<__nv_bfloat16*>(smem_raw);     // [BQ][ldq]
     __nv_bfloat16* ring = mixed + (size_t)BQ * ldq;                         // [STAGES][64][LDS]
-    int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    // eight warps: warps w and w + 4 share the 16 query rows of w and take the first and the second 32 keys of a page
+    int tid = threadIdx.x, warp = (tid >> 5) & 3, half = tid >> 7, lane = tid & 31, g = lane >> 2, t = lane & 3;
     const int* pages = block_table + (size_t)seq * table_stride;
 
     int row0 = tile * BQ + warp * 16 + g, row1 = row0 + 8;
@@ -212,13 +215,13 @@ sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
         __nv_bfloat16* to = ring + (size_t)(n % STAGES) * TILE_ELEMS;
         if (i < g_count) {
             const __nv_bfloat16* from = k_cache + ((page * n_kv_heads + g_first + i) * LLMB_PAGE) * D;
-            for (int c = tid; c < LLMB_PAGE * (D / 8); c += WARPS * 32) {
+            for (int c = tid; c < LLMB_PAGE * (D / 8); c += TILE_WARPS * 32) {
                 int row = c / (D / 8), col = (c % (D / 8)) * 8;
                 cp_async16(to + row * LDS + col, from + (size_t)row * D + col);
             }
         } else {
             const __nv_bfloat16* from = v_cache + ((page * n_kv_heads + kv_head) * LLMB_PAGE) * DV;
-            for (int c = tid; c < LLMB_PAGE * (DV / 8); c += WARPS * 32) {
+            for (int c = tid; c < LLMB_PAGE * (DV / 8); c += TILE_WARPS * 32) {
                 int row = c / (DV / 8), col = (c % (DV / 8)) * 8;
                 cp_async16(to + row * LDS + col, from + (size_t)row * DV + col);
             }
@@ -232,7 +235,7 @@ sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
     // the tile's mixed queries: for key head g, sum over the heads b of its group of talk[head, b] * q_b
     {
         int pairs = g_count * D / 2;
-        for (int idx = tid; idx < BQ * pairs; idx += WARPS * 32) {
+        for (int idx = tid; idx < BQ * pairs; idx += TILE_WARPS * 32) {
             int r = idx / pairs, c = (idx % pairs) * 2;
             int gi = c / D, d = c % D;
             int row = tile * BQ + r;
@@ -263,7 +266,7 @@ sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
     for (int n = 0; n < DV / 8; ++n)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[n][i] = 0.f;
-    float s[8][4];
+    float s[4][4];
 
     for (int n = 0; n < n_units; ++n) {
         cp_async_wait<1>();
@@ -276,7 +279,7 @@ sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
         const __nv_bfloat16* tile_s = ring + (size_t)(n % STAGES) * TILE_ELEMS;
         if (i == 0) {
 #pragma unroll
-            for (int nb = 0; nb < 8; ++nb)
+            for (int nb = 0; nb < 4; ++nb)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) s[nb][e] = 0.f;
         }
@@ -287,9 +290,9 @@ sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
                 uint32_t a[4];
                 ldmatrix_x4(a, a_base + kstep * 16);
 #pragma unroll
-                for (int nb = 0; nb < 8; nb += 2) {
+                for (int nb = 0; nb < 4; nb += 2) {
                     uint32_t b[4];
-                    int row = nb * 8 + (lane >> 4) * 8 + (lane & 7);
+                    int row = (half * 4 + nb) * 8 + (lane >> 4) * 8 + (lane & 7);
                     int col = kstep * 16 + ((lane >> 3) & 1) * 8;
                     ldmatrix_x4(b, tile_s + row * LDS + col);
                     mma_bf16(s[nb], a[0], a[1], a[2], a[3], b[0], b[1]);
@@ -302,13 +305,13 @@ sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
         bool edge = key0 + LLMB_PAGE - 1 > start + tile * BQ + warp * 16 ||
                     (window > 0 && key0 < start + tile * BQ + warp * 16 + 15 - window + 1);
 #pragma unroll
-        for (int nb = 0; nb < 8; ++nb) {
+        for (int nb = 0; nb < 4; ++nb) {
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 float w0 = __frcp_rn(1.0f + fast_exp2(fmaf(s[nb][e], slope, offset)));
                 float w1 = __frcp_rn(1.0f + fast_exp2(fmaf(s[nb][2 + e], slope, offset)));
                 if (edge) {
-                    int key = key0 + nb * 8 + 2 * t + e;
+                    int key = key0 + (half * 4 + nb) * 8 + 2 * t + e;
                     if (key > pos0 || key < low0) w0 = 0.f;
                     if (key > pos1 || key < low1) w1 = 0.f;
                 }
@@ -317,7 +320,7 @@ sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
             }
         }
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
+        for (int kk = 0; kk < 2; ++kk) {
             uint32_t pa0 = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
             uint32_t pa1 = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
             uint32_t pa2 = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
@@ -325,7 +328,7 @@ sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
 #pragma unroll
             for (int n2 = 0; n2 < DV / 8; n2 += 2) {
                 uint32_t b[4];
-                int row = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                int row = (half * 2 + kk) * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
                 int col = (n2 + (lane >> 4)) * 8;
                 ldmatrix_x4_trans(b, tile_s + row * LDS + col);
                 mma_bf16(acc[n2], pa0, pa1, pa2, pa3, b[0], b[1]);
@@ -334,6 +337,28 @@ sigmoid_attention_tiles_kernel(const __nv_bfloat16* __restrict__ q, int q_stride
         }
     }
     cp_async_wait<0>();
+    __syncthreads();                            // the ring is free: the second halves' sums pass through it
+    float* handover = reinterpret_cast<float*>(ring);          // [64 rows][DV]
+    if (half == 1) {
+#pragma unroll
+        for (int n = 0; n < DV / 8; ++n) {
+            float* to = handover + (size_t)(warp * 16 + g) * DV + n * 8 + 2 * t;
+            to[0] = acc[n][0];
+            to[1] = acc[n][1];
+            to[8 * DV] = acc[n][2];
+            to[8 * DV + 1] = acc[n][3];
+        }
+    }
+    __syncthreads();
+    if (half == 1) return;
+#pragma unroll
+    for (int n = 0; n < DV / 8; ++n) {
+        const float* from = handover + (size_t)(warp * 16 + g) * DV + n * 8 + 2 * t;
+        acc[n][0] += from[0];
+        acc[n][1] += from[1];
+        acc[n][2] += from[8 * DV];
+        acc[n][3] += from[8 * DV + 1];
+    }
 
     __nv_bfloat16* o0 = out + (size_t)(first_token + row0) * out_stride + (size_t)head * DV;
     __nv_bfloat16* o1 = out + (size_t)(first_token + row1) * out_stride + (size_t)head * DV;
@@ -362,7 +387,7 @@ static int launch_tiles(const void* q, int q_stride, const void* k_cache, const 
         configured = smem;
     }
     dim3 grid(n_heads, (max_new + BQ - 1) / BQ, n_seqs);
-    sigmoid_attention_tiles_kernel<D, DV><<<grid, WARPS * 32, smem, stream>>>(
+    sigmoid_attention_tiles_kernel<D, DV><<<grid, TILE_WARPS * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_table,
         table_stride, ring_pages, cu_seqlens, seq_lens, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale, window,
         talk, head_bias, out_scale);

@@ -979,7 +979,7 @@ def sigmoid_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok
 
 
 def gated_recurrence(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_bias, rate, state, tok_seq,
-                     cu_seqlens, slot_ids, out, out_scale, work):
+                     cu_seqlens, slot_ids, out, out_scale, work, single_tokens=False):
     """A real-gated linear recurrence behind a short causal convolution, on C channels. `y`, `x`
     [T, C] (the run's dtype; rows contiguous, may be column ranges): the two branches' projections
     with their biases. u = conv_b + sum_j conv_w[:, j] * x[t - (taps - 1) + j] over the tokens of
@@ -991,7 +991,7 @@ def gated_recurrence(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_b
     [slots, taps, C]: rows 0 .. taps - 2 the convolution's last inputs (oldest first), the last row
     S; it is read at the slot of each sequence and brought up to date. `work` float32 [3, T, C]:
     u, a and the driving term of every token, between the three kernels. Everything but the rounding of
-    `out` is 32-bit."""
+    `out` is 32-bit. `single_tokens`: every sequence brings exactly one token (token b is sequence b's)."""
     _require_cuda(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_bias, rate, state, tok_seq, cu_seqlens,
                   slot_ids, out, work)
     n, channels = y.shape
@@ -1013,7 +1013,8 @@ def gated_recurrence(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_b
           _c_int(_code(y.dtype)), _ptr(conv_w), _ptr(conv_b), _c_int(taps), _ptr(gate_a), _ptr(gate_a_bias),
           _ptr(gate_i), _ptr(gate_i_bias), _c_int(blocks), _ptr(rate), _ptr(state), _ptr(tok_seq), _ptr(cu_seqlens),
           _ptr(slot_ids), _ptr(out), _c_int(out.stride(0)), _c_float(out_scale), _ptr(work), _c_int(n),
-          _c_int(channels), _c_int(cu_seqlens.numel() - 1), _stream(), kernels=3)
+          _c_int(channels), _c_int(cu_seqlens.numel() - 1), _c_int(1 if single_tokens else 0), _stream(),
+          kernels=3 if n <= 256 else 5)
     return out
 
 

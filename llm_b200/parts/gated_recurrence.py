@@ -74,9 +74,12 @@ class GatedRecurrenceMixer(ProjectedMixer):
     def state_request(self):
         return StateRequest((self.spec.conv_taps, self.spec.width), torch.float32)
 
+    def mix_replay_key(self, step):
+        return (bool(step.decode),)
+
     def mix_scratch(self, n_tokens, dtype):
         from ..engine.workspace import BufferRequest
-        # phase 0: both kernels (the scan reads what the gates wrote)
+        # phase 0: all kernels (the scan reads what the gates wrote)
         return [BufferRequest("decay_drive", (3, n_tokens, self.spec.width), torch.float32, 0, 0)]
 
     def mix(self, proj, ctx, entry, cache_entry, out, scratch):
@@ -87,7 +90,8 @@ class GatedRecurrenceMixer(ProjectedMixer):
             work = torch.empty((3, n, s.width), dtype=torch.float32, device=proj.device)
         ops.gated_recurrence(proj[:, :s.width], proj[:, s.width:], self.conv, self.conv_bias, self.gate_a,
                              self.gate_a_bias, self.gate_i, self.gate_i_bias, self.rate, ctx.cache.state_view(entry),
-                             ctx.tok_seq, ctx.cu_seqlens, ctx.slot_ids, out, s.out_scale, work)
+                             ctx.tok_seq, ctx.cu_seqlens, ctx.slot_ids, out, s.out_scale, work,
+                             single_tokens=ctx.decode)
 
 
 register_mixer("gated_recurrence", GatedRecurrenceMixer)

@@ -229,7 +229,7 @@ def sigmoid_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok
 
 
 def gated_recurrence(y, x, conv_w, conv_b, gate_a, gate_a_bias, gate_i, gate_i_bias, rate, state, tok_seq,
-                     cu_seqlens, slot_ids, out, out_scale, work):
+                     cu_seqlens, slot_ids, out, out_scale, work, single_tokens=False):
     """Sequence by sequence and token by token. state [slots, taps, C] float32: rows 0 .. taps - 2
     are the convolution's last inputs (oldest first), the last row is S."""
     n, channels = y.shape

@@ -342,7 +342,8 @@ def _recurrence(fn, wide, params, state, batch, channels, dtype):
     work = torch.empty((3, batch.n_tokens, channels), device=DEV)
     p = params
     fn(wide[:, 2:2 + channels], wide[:, 2 + channels:2 + 2 * channels], p["conv_w"], p["conv_b"], p["gate_a"], p["gate_a_bias"],
-       p["gate_i"], p["gate_i_bias"], p["rate"], state, batch.tok_seq, batch.cu, batch.slots, out_wide[:, 4:4 + channels], 0.9, work)
+       p["gate_i"], p["gate_i_bias"], p["rate"], state, batch.tok_seq, batch.cu, batch.slots, out_wide[:, 4:4 + channels], 0.9, work,
+       single_tokens=all(k == 1 for k in batch.new))
     return out_wide
 
 
