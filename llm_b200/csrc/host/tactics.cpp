@@ -207,7 +207,8 @@ const std::vector<Row>& table(int family) {
         {"sigmoid_attention_decode", 20, sigmoid_decode_guard,
          "one token a sequence: a block serves a slice of a sequence's pages for ALL heads (the heads are the rows of "
          "the mma.sync tiles, the mixed queries of all heads lie in shared memory), so the window's keys and values "
-         "are read once; key and value tiles of all kv heads through a ring of four buffers; slices add in a fixed order"},
+         "are read once; the mixed queries are formed once a step by a small kernel; key and value tiles of all kv heads through "
+         "two buffers (two blocks an SM); slices add in a fixed order"},
         {"sigmoid_attention_tiles", 10, sigmoid_tiles_guard,
          "tiles of 64 queries of one head on mma.sync over the pages the tile's windows reach; the mix over the heads "
          "is done on the queries (a mixed query of kv heads x head size elements in shared memory), the key tiles of "

@@ -425,19 +425,44 @@ LLMB_EXPORT int llmb_sigmoid_attention_tiles(const void* q, int q_stride, const 
 // sigmoid_attention_decode: a step in which every sequence brings one token is bound by reading the keys and
 // values of the window once. A block serves one (slice of the pages, sequence) for ALL heads: the heads are the
 // rows of the tensor-core tiles (16 * MT of them), the mixed queries of all heads lie in shared memory, and per
-// page the G key tiles and the G value tiles stream through a ring of four buffers. Each warp takes 16 of a
+// page the G key tiles and the G value tiles stream through two buffers (two blocks share an SM). Each warp takes 16 of a
 // page's 64 keys; the weights of a head go into the second product only with the value tile of the head's own
 // group (the other rows of the operand are zero). Nothing is normalised, so the slices' results simply add: the
 // four warps are added in a fixed order, and with more than one slice a second kernel adds the slices in order.
-constexpr int DECODE_STAGES = 4;
+constexpr int DECODE_STAGES = 2;
+
+// The mixed queries of a step of one token a sequence, once for all slices: mixed[seq][a][g * D + d] =
+// sum over the heads b of group g of talk[a, b] * q[seq][b][d] (rows beyond the heads are zero).
+__global__ void __launch_bounds__(128)
+sigmoid_attention_mix_queries_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const float* __restrict__ talk,
+                                     __nv_bfloat16* __restrict__ mixed, int rows, int n_heads, int n_kv_heads, int dim) {
+    griddep_launch();
+    griddep_wait();
+    int seq = blockIdx.x, a = blockIdx.y;
+    int group = n_heads / n_kv_heads, width = n_kv_heads * dim;
+    const __nv_bfloat16* q_row = q + (size_t)seq * q_stride;
+    __nv_bfloat16* to = mixed + ((size_t)seq * rows + a) * width;
+    for (int c = threadIdx.x; c < width; c += 128) {
+        int gi = c / dim, d = c % dim;
+        float sum = 0.f;
+        if (a < n_heads) {
+            for (int b = 0; b < group; ++b) {
+                int other = gi * group + b;
+                float w = talk ? talk[(size_t)a * n_heads + other] : (other == a ? 1.f : 0.f);
+                sum = fmaf(w, to_float(q_row[(size_t)other * dim + d]), sum);
+            }
+        }
+        to[c] = __float2bfloat16_rn(sum);
+    }
+}
 
 template <int D, int DV, int MT>
 __global__ void __launch_bounds__(WARPS * 32)
-sigmoid_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const __nv_bfloat16* __restrict__ k_cache,
+sigmoid_attention_decode_kernel(const __nv_bfloat16* __restrict__ mixed_queries, const __nv_bfloat16* __restrict__ k_cache,
                                 const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                                 int table_stride, int ring_pages, const int* __restrict__ seq_lens,
                                 __nv_bfloat16* __restrict__ out, int out_stride, float* __restrict__ partial,
-                                int n_heads, int n_kv_heads, float scale, int window, const float* __restrict__ talk,
+                                int n_heads, int n_kv_heads, float scale, int window,
                                 const float* __restrict__ head_bias, float out_scale) {
     constexpr int LDS = (D > DV ? D : DV) + PAD;
     constexpr int TILE_ELEMS = LLMB_PAGE * LDS;
@@ -479,29 +504,18 @@ sigmoid_attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_strid
             }
         }
     };
+    {   // the sequence's mixed queries (made once a step by the kernel before this one) join the first group of copies
+        int chunks = g_count * D / 8;
+        const __nv_bfloat16* from = mixed_queries + (size_t)seq * ROWS * g_count * D;
+        for (int c = tid; c < ROWS * chunks; c += WARPS * 32) {
+            int row = c / chunks, col = (c % chunks) * 8;
+            cp_async16(mixed + (size_t)row * ldq + col, from + (size_t)row * g_count * D + col);
+        }
+    }
 #pragma unroll
     for (int n = 0; n < DECODE_STAGES - 1; ++n) {
         if (n < n_units) load_unit(n);
         cp_async_commit();
-    }
-    // the mixed queries of all heads: row a, key head g: sum over the heads b of group g of talk[a, b] * q_b
-    {
-        const __nv_bfloat16* q_row = q + (size_t)seq * q_stride;
-        int pairs = g_count * D / 2;
-        for (int idx = tid; idx < ROWS * pairs; idx += WARPS * 32) {
-            int a = idx / pairs, c = (idx % pairs) * 2;
-            int gi = c / D, d = c % D;
-            float lo = 0.f, hi = 0.f;
-            if (a < n_heads) {
-                for (int b = 0; b < group; ++b) {
-                    int other = gi * group + b;
-                    float w = talk ? talk[(size_t)a * n_heads + other] : (other == a ? 1.f : 0.f);
-                    lo = fmaf(w, to_float(q_row[(size_t)other * D + d]), lo);
-                    hi = fmaf(w, to_float(q_row[(size_t)other * D + d + 1]), hi);
-                }
-            }
-            *reinterpret_cast<__nv_bfloat162*>(mixed + (size_t)a * ldq + c) = __floats2bfloat162_rn(lo, hi);
-        }
     }
     float slope = -scale * 1.4426950408889634f;
     float offset0[MT], offset1[MT];                  // -bias log2 e of this lane's two rows of every row tile
@@ -643,10 +657,15 @@ static int launch_decode(const void* q, int q_stride, const void* k_cache, const
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
+    // the scratch begins with the mixed queries (bfloat16 [n_seqs][ROWS][kv heads * D]); the slices' sums follow
+    __nv_bfloat16* mixed = reinterpret_cast<__nv_bfloat16*>(scratch);
+    scratch += ((size_t)n_seqs * ROWS * n_kv_heads * D + 1) / 2;
+    LLMB_CUDA(llmb::launch(sigmoid_attention_mix_queries_kernel, dim3(n_seqs, ROWS), dim3(128), 0, stream, true,
+                           (const __nv_bfloat16*)q, q_stride, talk, mixed, ROWS, n_heads, n_kv_heads, D));
     LLMB_CUDA(llmb::launch(sigmoid_attention_decode_kernel<D, DV, MT>, dim3(n_splits, n_seqs), dim3(WARPS * 32), smem, stream,
-                           true, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
+                           true, (const __nv_bfloat16*)mixed, (const __nv_bfloat16*)k_cache,
                            (const __nv_bfloat16*)v_cache, block_table, table_stride, ring_pages, seq_lens,
-                           (__nv_bfloat16*)out, out_stride, scratch, n_heads, n_kv_heads, scale, window, talk, head_bias,
+                           (__nv_bfloat16*)out, out_stride, scratch, n_heads, n_kv_heads, scale, window, head_bias,
                            out_scale));
     if (n_splits > 1) {
         int width = n_heads * DV;
@@ -656,8 +675,9 @@ static int launch_decode(const void* q, int q_stride, const void* k_cache, const
     return check_launch("sigmoid_attention_decode");
 }
 
-// One query a sequence (row b of q is sequence b's, at position seq_lens[b] - 1). scratch: n_seqs * n_splits *
-// n_heads * vdim floats where n_splits > 1. Up to 32 heads.
+// One query a sequence (row b of q is sequence b's, at position seq_lens[b] - 1). scratch: the mixed queries
+// (n_seqs * (16 or 32 rows) * n_kv_heads * dim bfloat16) and, where n_splits > 1, n_seqs * n_splits * n_heads * vdim
+// floats. Up to 32 heads.
 LLMB_EXPORT int llmb_sigmoid_attention_decode(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                                               const int* block_table, int table_stride, int ring_pages,
                                               const int* seq_lens, void* out, int out_stride, float* scratch,
@@ -669,7 +689,8 @@ LLMB_EXPORT int llmb_sigmoid_attention_decode(const void* q, int q_stride, const
                  "sigmoid_attention_decode: %d heads over %d kv heads (up to 32 heads)", n_heads, n_kv_heads);
     LLMB_REQUIRE(n_seqs <= 65535 && n_splits >= 1 && n_splits <= 65535 && ring_pages > 0 && window >= 0,
                  "sigmoid_attention_decode: bad sizes");
-    LLMB_REQUIRE(n_splits == 1 || (scratch && scratch_floats >= (long long)n_seqs * n_splits * n_heads * vdim),
+    long long mixed_floats = ((long long)n_seqs * (n_heads <= 16 ? 16 : 32) * n_kv_heads * dim + 1) / 2;
+    LLMB_REQUIRE(scratch && scratch_floats >= mixed_floats + (n_splits > 1 ? (long long)n_seqs * n_splits * n_heads * vdim : 0),
                  "sigmoid_attention_decode: scratch too small");
 #define X(DK, DVAL)                                                                                                   \
     if (dim == DK && vdim == DVAL) {                                                                                  \

@@ -948,7 +948,7 @@ def sigmoid_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok
         q.stride(0) % 2 == 0 and out.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0 and out.data_ptr() % 4 == 0)
     if variant == "sigmoid_attention_decode":
         splits = sigmoid_decode_splits(n, max_len, window)
-        need = n * splits * n_heads * vdim if splits > 1 else 0
+        need = (n * (16 if n_heads <= 16 else 32) * n_kv_heads * dim + 1) // 2 + (n * splits * n_heads * vdim if splits > 1 else 0)
         scratch = _attention_scratch.get(q.device)
         if scratch is None or scratch.numel() < need:
             if scratch is not None:
@@ -961,7 +961,7 @@ def sigmoid_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok
               _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(seq_lens),
               _ptr(out), _c_int(out.stride(0)), _ptr(scratch), ctypes.c_longlong(scratch.numel()), _c_int(n),
               _c_int(n_heads), _c_int(n_kv_heads), _c_int(dim), _c_int(vdim), _c_float(scale), _c_int(window),
-              _ptr(talk), _ptr(head_bias), _c_float(out_scale), _c_int(splits), _stream(), kernels=2 if splits > 1 else 1)
+              _ptr(talk), _ptr(head_bias), _c_float(out_scale), _c_int(splits), _stream(), kernels=3 if splits > 1 else 2)
         return out
     if variant == "sigmoid_attention_tiles":
         _call("sigmoid_attention", "llmb_sigmoid_attention_tiles", _ptr(q), _c_int(q.stride(0)), _ptr(k_cache),
