@@ -21,16 +21,8 @@
 //   acc) and the four are merged once at the end in a fixed order;
 // * rows of the tile are the query heads of the group: up to 8.
 //
-// * a group of more than 8 query heads is served as several blocks of up to 8 rows over the same
-//   key/value head (grid.y = kv heads x chunks);
-// * with a window w the query at position len - 1 sees the keys from len - w on: the slices are an
-//   even share of the pages from that key's page on, and keys before it are masked;
-// * optional, applied where the result is written (by the block itself with one slice, else by the
-//   combining kernel), in 32-bit: `sinks` [heads] (e^sink joins the head's denominator), `gate`
-//   [sequences, heads] (times sigmoid(gate)), `out_scale`. When the value cache IS the key cache, a
-//   page is fetched once and both products read the same tile.
-//
-// Refused (the generic kernel serves them): head sizes other than 32, 64, 96, 128, 32-bit caches.
+// Refused (the generic kernel serves them): a window, groups above 8, head
+// sizes that are no multiple of 16 or exceed 128, 32-bit caches.
 #include "common.cuh"
 #include "mma.cuh"
 
@@ -54,25 +46,6 @@ __host__ __device__ constexpr int stages_for() {
     return fit < 3 ? 3 : fit > 8 ? 8 : fit;
 }
 
-// The result of a head from its weighted values, their reference m (base-2 units) and the sum of the weights:
-// a sink joins the denominator (and becomes the reference where it is larger, so that nothing overflows), then
-// the gate and the scale.
-__device__ __forceinline__ float finished(float value, float m, float sum, int head, int seq,
-                                          const float* __restrict__ sinks, const __nv_bfloat16* __restrict__ gate,
-                                          int gate_stride, float out_scale) {
-    float result;
-    if (sinks) {
-        float sink2 = sinks[head] * 1.4426950408889634f;
-        float reference = fmaxf(m, sink2);
-        float w = exp2f(m - reference);
-        result = value * w / (sum * w + exp2f(sink2 - reference));
-    } else {
-        result = value / sum;
-    }
-    if (gate) result *= 1.0f / (1.0f + expf(-to_float(gate[(size_t)seq * gate_stride + head])));
-    return out_scale == 1.0f ? result : result * out_scale;
-}
-
 // partial layout: acc [seq, head, split, D] floats; stats [seq, head, split, 2] = (max, sum),
 // max in base-2 units (score * scale * log2 e).
 template <int D>
@@ -84,11 +57,8 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
                               const int* __restrict__ seq_lens, const int* __restrict__ seq_order,
                               float* __restrict__ part_acc, float* __restrict__ part_stats,
                               __nv_bfloat16* __restrict__ out, int out_stride,
-                              int n_heads, int n_kv_heads, float scale_log2, int window, int chunks,
-                              const float* __restrict__ sinks, const __nv_bfloat16* __restrict__ gate,
-                              int gate_stride, float out_scale) {
+                              int n_heads, int n_kv_heads, float scale_log2) {
     constexpr int LDS = D + PAD;
-    const bool values_are_keys = k_cache == v_cache;
     constexpr int PAGE_ELEMS = LLMB_PAGE * LDS;
     constexpr int STAGES = stages_for<D>();
     constexpr int UNIT = pages_per_stage<D>();
@@ -104,18 +74,14 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     LLMB_STAMP(0, 0);                               // the block has started
     // blocks start in the order of blockIdx; seq_order (optional) lists the sequences by falling
     // length, so that the longest ones start first and the short ones fill the end of the step
-    int split = blockIdx.x, n_splits = gridDim.x, kv_head = blockIdx.y / chunks;
+    int split = blockIdx.x, n_splits = gridDim.x, kv_head = blockIdx.y;
     int seq = seq_order ? seq_order[blockIdx.z] : (int)blockIdx.z;
-    int whole_group = n_heads / n_kv_heads;
-    int head_base = kv_head * whole_group + (blockIdx.y % chunks) * 8;      // this block's first query head
-    int group = min(8, whole_group - (int)(blockIdx.y % chunks) * 8);          // and how many it serves
+    int group = n_heads / n_kv_heads;
     int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
     int len = seq_lens[seq];
-    int oldest = window > 0 ? max(len - window, 0) : 0;             // the first key the query sees
-    int first_page = oldest / LLMB_PAGE;
     int n_pages = (len + LLMB_PAGE - 1) / LLMB_PAGE;
-    int per_split = (n_pages - first_page + n_splits - 1) / n_splits;
-    int page_begin = min(first_page + split * per_split, n_pages);
+    int per_split = (n_pages + n_splits - 1) / n_splits;
+    int page_begin = min(split * per_split, n_pages);
     int page_end = min(page_begin + per_split, n_pages);
     const int* pages = block_table + (size_t)seq * table_stride;
 
@@ -128,7 +94,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         for (int c = tid; c < LLMB_PAGE * CHUNKS_PER_ROW; c += WARPS * 32) {
             int row = c / CHUNKS_PER_ROW, col = (c % CHUNKS_PER_ROW) * 8;
             cp_async16(ks + row * LDS + col, k_cache + base + (size_t)row * D + col);
-            if (!values_are_keys) cp_async16(vs + row * LDS + col, v_cache + base + (size_t)row * D + col);
+            cp_async16(vs + row * LDS + col, v_cache + base + (size_t)row * D + col);
         }
     };
     int n_my = page_end - page_begin;
@@ -163,7 +129,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
     // Q fragments of this warp's lane: row g = head kv_head * group + g (zero beyond the group)
     uint32_t qa0[D / 16], qa2[D / 16];
     {
-        const __nv_bfloat16* q_row = q + (size_t)seq * q_stride + (size_t)(head_base + g) * D;
+        const __nv_bfloat16* q_row = q + (size_t)seq * q_stride + (size_t)(kv_head * group + g) * D;
         bool valid = g < group;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
@@ -193,10 +159,10 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         int logical = page_begin + i * UNIT + place;
         if (logical >= page_end) break;
         const __nv_bfloat16* ks = smem + (size_t)(i % STAGES) * STAGE_ELEMS + (size_t)place * 2 * PAGE_ELEMS;
-        const __nv_bfloat16* vs = values_are_keys ? ks : ks + PAGE_ELEMS;
+        const __nv_bfloat16* vs = ks + PAGE_ELEMS;
         int key_base = warp * 16;
         int first_key = logical * LLMB_PAGE + key_base;
-        if (first_key >= len || first_key + 16 <= oldest) continue;     // none of this warp's 16 keys is seen
+        if (first_key >= len) continue;             // this warp's 16 keys are all beyond the sequence
 
         float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -214,7 +180,7 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
         float local_max = -INFINITY;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            v[j] = (key[j] < len && key[j] >= oldest) ? v[j] * scale_log2 : -INFINITY;
+            v[j] = key[j] < len ? v[j] * scale_log2 : -INFINITY;
             local_max = fmaxf(local_max, v[j]);
         }
         local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, 1));
@@ -271,11 +237,10 @@ attention_decode_split_kernel(const __nv_bfloat16* __restrict__ q, int q_stride,
             sum += merge_sum[w * 8 + head] * weight;
         }
         if (n_splits == 1) {                          // nothing to combine: this is the result
-            out[(size_t)seq * out_stride + (size_t)(head_base + head) * D + d] =
-                __float2bfloat16_rn(finished(value, m, sum, head_base + head, seq, sinks, gate, gate_stride, out_scale));
+            out[(size_t)seq * out_stride + (size_t)(kv_head * group + head) * D + d] = __float2bfloat16_rn(value / sum);
             continue;
         }
-        size_t slot = ((size_t)seq * n_heads + head_base + head) * n_splits + split;
+        size_t slot = ((size_t)seq * n_heads + kv_head * group + head) * n_splits + split;
         part_acc[slot * D + d] = value;
         if (d == 0) { part_stats[slot * 2] = m; part_stats[slot * 2 + 1] = sum; }
     }
@@ -286,9 +251,7 @@ template <int D>
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_acc,
                                                 const float* __restrict__ part_stats,
                                                 __nv_bfloat16* __restrict__ out, int out_stride,
-                                                int n_heads, int n_splits, const float* __restrict__ sinks,
-                                                const __nv_bfloat16* __restrict__ gate, int gate_stride,
-                                                float out_scale) {
+                                                int n_heads, int n_splits) {
     griddep_launch();
     griddep_wait();
     int seq = blockIdx.y, head = blockIdx.x;
@@ -303,8 +266,7 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_a
             value += part_acc[(base + s) * D + d] * weight;
             sum += part_stats[(base + s) * 2 + 1] * weight;
         }
-        out[(size_t)seq * out_stride + (size_t)head * D + d] =
-            __float2bfloat16_rn(finished(value, m, sum, head, seq, sinks, gate, gate_stride, out_scale));
+        out[(size_t)seq * out_stride + (size_t)head * D + d] = __float2bfloat16_rn(value / sum);
     }
 }
 
@@ -312,8 +274,7 @@ template <int D>
 static int launch(const void* q, int q_stride, const void* k_cache, const void* v_cache,
                   const int* block_table, int table_stride, int ring_pages, const int* seq_lens,
                   const int* seq_order, void* out, int out_stride, float* scratch, int n_seqs, int n_heads,
-                  int n_kv_heads, float scale, int window, const float* sinks, const void* gate, int gate_stride,
-                  float out_scale, int n_splits, cudaStream_t stream) {
+                  int n_kv_heads, float scale, int n_splits, cudaStream_t stream) {
     constexpr int LDS = D + PAD;
     constexpr int STAGES = stages_for<D>();
     size_t stage_bytes = (size_t)STAGES * pages_per_stage<D>() * 2 * LLMB_PAGE * LDS * sizeof(__nv_bfloat16);
@@ -327,18 +288,15 @@ static int launch(const void* q, int q_stride, const void* k_cache, const void* 
     }
     float* part_acc = scratch;
     float* part_stats = scratch + (size_t)n_seqs * n_heads * n_splits * D;
-    int chunks = (n_heads / n_kv_heads + 7) / 8;
-    dim3 grid(n_splits, n_kv_heads * chunks, n_seqs);
+    dim3 grid(n_splits, n_kv_heads, n_seqs);
     llmb::launch(attention_decode_split_kernel<D>, grid, WARPS * 32, smem, stream, true,
                  (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_cache,
                  (const __nv_bfloat16*)v_cache, block_table, table_stride, ring_pages, seq_lens, seq_order,
-                 part_acc, part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f,
-                 window, chunks, sinks, (const __nv_bfloat16*)gate, gate_stride, out_scale);
+                 part_acc, part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_kv_heads, scale * 1.4426950408889634f);
     int code = check_launch("attention_decode_split");
     if (code || n_splits == 1) return code;
     llmb::launch(attention_decode_combine_kernel<D>, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, true,
-                 (const float*)part_acc, (const float*)part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_splits,
-                 sinks, (const __nv_bfloat16*)gate, gate_stride, out_scale);
+                 (const float*)part_acc, (const float*)part_stats, (__nv_bfloat16*)out, out_stride, n_heads, n_splits);
     return check_launch("attention_decode_combine");
 }
 
@@ -354,9 +312,9 @@ LLMB_EXPORT long long llmb_attention_decode_scratch_floats(int n_seqs, int n_hea
 
 // Whether the kernel serves this shape; the text of the refusal is in last_error.
 LLMB_EXPORT int llmb_attention_decode_supports(int n_heads, int n_kv_heads, int head_dim, int window) {
-    LLMB_REQUIRE(window >= 0, "attention_decode: a window of %d", window);
-    LLMB_REQUIRE(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && (long long)n_kv_heads * ((n_heads / n_kv_heads + 7) / 8) <= 65535,
-                 "attention_decode: %d heads over %d kv heads", n_heads, n_kv_heads);
+    LLMB_REQUIRE(window == 0, "attention_decode: a window of %d is not served", window);
+    LLMB_REQUIRE(n_kv_heads > 0 && n_heads % n_kv_heads == 0 && n_heads / n_kv_heads <= 8,
+                 "attention_decode: %d heads over %d kv heads (groups up to 8)", n_heads, n_kv_heads);
     LLMB_REQUIRE(head_dim == 32 || head_dim == 64 || head_dim == 96 || head_dim == 128,
                  "attention_decode: head_dim %d (served: 32, 64, 96, 128)", head_dim);
     return LLMB_OK;
@@ -367,8 +325,7 @@ LLMB_EXPORT int llmb_attention_decode(const void* q, int q_stride, const void* k
                                       int ring_pages, const int* seq_lens, const int* seq_order, void* out,
                                       int out_stride, float* scratch, long long scratch_floats, int n_seqs,
                                       int n_heads, int n_kv_heads, int head_dim, float scale,
-                                      int window, const float* sinks, const void* gate, int gate_stride,
-                                      float out_scale, int n_splits, cudaStream_t stream) {
+                                      int window, int n_splits, cudaStream_t stream) {
     if (n_seqs == 0) return LLMB_OK;
     int code = llmb_attention_decode_supports(n_heads, n_kv_heads, head_dim, window);
     if (code) return code;
@@ -380,8 +337,7 @@ LLMB_EXPORT int llmb_attention_decode(const void* q, int q_stride, const void* k
                                                              n_seqs, n_heads, head_dim, n_splits),
                  "attention_decode: scratch too small");
 #define ARGS q, q_stride, k_cache, v_cache, block_table, table_stride, ring_pages, seq_lens, seq_order, out, \
-             out_stride, scratch, n_seqs, n_heads, n_kv_heads, scale, window, sinks, gate, gate_stride, out_scale, \
-             n_splits, stream
+             out_stride, scratch, n_seqs, n_heads, n_kv_heads, scale, n_splits, stream
     switch (head_dim) {
         case 32: return launch<32>(ARGS);
         case 64: return launch<64>(ARGS);

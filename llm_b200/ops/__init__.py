@@ -24,7 +24,7 @@ from . import tactics
 from .build import all_sources, ensure_built, load_library
 
 PAGE = native.plan_constant("page")              # positions per cache page (csrc/plan.h)
-BFLOAT16_ONLY = ("gemm_tc", "gemm_skinny", "attention_decode", "attention_prefill",
+BFLOAT16_ONLY = ("gemm_tc", "gemm_skinny", "attention_decode", "attention_decode_window", "attention_prefill",
                  "attention_prefill_tc")     # (diff_attention holds the 32-bit kernel too)
 
 _DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1}
@@ -864,11 +864,16 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
               _c_int(head_dim), _c_float(scale), _c_int(window), _ptr(sinks), _ptr(gate),
               _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _stream())
     elif variant == "attention_decode":
+        # the plain grouped-query case keeps the kernel file it was tuned in; a window, a sink, a gate, a scale, a
+        # value cache that is the key cache and groups above 8 run the same kernel with those additions
+        plain = (window == 0 and sinks is None and gate is None and out_scale == 1.0 and n_heads // n_kv_heads <= 8
+                 and k_cache.data_ptr() != v_cache.data_ptr())
+        name = "attention_decode" if plain else "attention_decode_window"
         splits = attention_decode_splits(n, n_heads, n_kv_heads, max_len, window)
-        lib = load_library("attention_decode")
-        lib.llmb_attention_decode_scratch_floats.restype = ctypes.c_longlong
-        need = lib.llmb_attention_decode_scratch_floats(_c_int(n), _c_int(n_heads), _c_int(head_dim),
-                                                        _c_int(splits))
+        lib = load_library(name)
+        sizer = getattr(lib, f"llmb_{name}_scratch_floats")
+        sizer.restype = ctypes.c_longlong
+        need = sizer(_c_int(n), _c_int(n_heads), _c_int(head_dim), _c_int(splits))
         scratch = _attention_scratch.get(qkv.device)
         if scratch is None or scratch.numel() < need:
             if scratch is not None:
@@ -877,14 +882,16 @@ def attention(qkv, k_cache, v_cache, block_table, ring_pages, tok_pos, tok_seq, 
                 _scratch_generation += 1
             scratch = torch.empty(max(need, 1 << 23), dtype=torch.float32, device=qkv.device)
             _attention_scratch[qkv.device] = scratch
-        _call("attention_decode", "llmb_attention_decode", _ptr(qkv), _c_int(qkv.stride(0)),
-              _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),
-              _c_int(ring_pages), _ptr(seq_lens), _ptr(seq_order), _ptr(out), _c_int(out.stride(0)),
-              _ptr(scratch),
-              ctypes.c_longlong(scratch.numel()), _c_int(n), _c_int(n_heads), _c_int(n_kv_heads),
-              _c_int(head_dim), _c_float(scale), _c_int(window), _ptr(sinks), _ptr(gate),
-              _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _c_int(splits), _stream(),
-              kernels=2 if splits > 1 else 1)
+        head = (_ptr(qkv), _c_int(qkv.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_table),
+                _c_int(block_table.shape[1]), _c_int(ring_pages), _ptr(seq_lens), _ptr(seq_order), _ptr(out),
+                _c_int(out.stride(0)), _ptr(scratch), ctypes.c_longlong(scratch.numel()), _c_int(n), _c_int(n_heads),
+                _c_int(n_kv_heads), _c_int(head_dim), _c_float(scale), _c_int(window))
+        if plain:
+            _call(name, "llmb_attention_decode", *head, _c_int(splits), _stream(), kernels=2 if splits > 1 else 1)
+        else:
+            _call(name, "llmb_attention_decode_window", *head, _ptr(sinks), _ptr(gate),
+                  _c_int(gate.stride(0) if gate is not None else 0), _c_float(out_scale), _c_int(splits), _stream(),
+                  kernels=2 if splits > 1 else 1)
     elif variant == "attention_generic":
         _call("attention_generic", "llmb_attention_generic", _ptr(qkv), _c_int(qkv.stride(0)),
               _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _c_int(block_table.shape[1]),

@@ -17,7 +17,7 @@ class AttentionMixer(Mixer):
     scale, the window, the biases and the position encoding as parameters."""
     graph_safe = True
     emits = True
-    libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "attention_generic", "attention_decode", "attention_prefill", "attention_prefill_tc")
+    libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "attention_generic", "attention_decode", "attention_decode_window", "attention_prefill", "attention_prefill_tc")
 
     def __init__(self, spec):
         self.spec = spec

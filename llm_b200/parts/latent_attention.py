@@ -27,7 +27,7 @@ class LatentAttentionMixer(ProjectedMixer):
     (ops.norm_rope_cache_write), the query product, the attention with sink, gate and scale in its
     epilogue (ops.attention), the output product."""
     libraries = ("elementwise", "gemm_simt", "gemm_skinny", "gemm_tc", "projection_norm", "attention_generic",
-                 "attention_decode", "attention_prefill")
+                 "attention_decode", "attention_decode_window", "attention_prefill")
 
     def __init__(self, spec):
         s = spec
