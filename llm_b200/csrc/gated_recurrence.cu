@@ -91,9 +91,11 @@ gates_kernel(const float* __restrict__ u, int channels, const float* __restrict_
                   const float* __restrict__ gate_i, const float* __restrict__ gate_i_bias, int part,
                   const float* __restrict__ rate, float* __restrict__ decay, float* __restrict__ drive, int n_tokens) {
     constexpr int TM = 16 * TT;
-    __shared__ __align__(16) float u_tile[KC][TM];          // [input channel][token]
-    __shared__ __align__(16) float a_tile[KC][TN];          // [input channel][output channel]
-    __shared__ __align__(16) float i_tile[KC][TN];
+    // rows padded by four floats: a thread's 16-byte reads stay aligned, and the stores (16 neighbouring threads
+    // write one column) spread over the banks
+    __shared__ __align__(16) float u_tile[KC][TM + 4];      // [input channel][token]
+    __shared__ __align__(16) float a_tile[KC][TN + 4];      // [input channel][output channel]
+    __shared__ __align__(16) float i_tile[KC][TN + 4];
     griddep_launch();
     griddep_wait();
     int tiles_per_part = (part + TN - 1) / TN;
@@ -109,20 +111,42 @@ gates_kernel(const float* __restrict__ u, int channels, const float* __restrict_
         for (int n = 0; n < 4; ++n) acc_a[m][n] = acc_i[m][n] = 0.f;
     const float* wa = gate_a + (size_t)b * part * part;
     const float* wi = gate_i + (size_t)b * part * part;
-    for (int k0 = 0; k0 < part; k0 += KC) {
-        for (int e = threadIdx.x; e < TM * KC; e += 256) {
+    // the next chunk's values are requested into registers before this chunk's products run
+    constexpr int U_PER = TM * KC / 256, W_PER = TN * KC / 256;
+    float u_next[U_PER], a_next[W_PER], i_next[W_PER];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int j = 0; j < U_PER; ++j) {
+            int e = threadIdx.x + j * 256;
             int m = e / KC, k = e % KC;                 // neighbouring threads: neighbouring channels of one token
             int t = t0 + m;
-            u_tile[k][m] = (t < n_tokens && k0 + k < part) ? u[(size_t)t * channels + b * part + k0 + k] : 0.f;
+            u_next[j] = (t < n_tokens && k0 + k < part) ? u[(size_t)t * channels + b * part + k0 + k] : 0.f;
         }
-        for (int e = threadIdx.x; e < TN * KC; e += 256) {
+#pragma unroll
+        for (int j = 0; j < W_PER; ++j) {
+            int e = threadIdx.x + j * 256;
             int n = e / KC, k = e % KC;                 // neighbouring threads: neighbouring inputs of one output row
             bool live = o0 + n < part && k0 + k < part;
             size_t at = (size_t)(o0 + n) * part + k0 + k;
-            a_tile[k][n] = live ? wa[at] : 0.f;
-            i_tile[k][n] = live ? wi[at] : 0.f;
+            a_next[j] = live ? wa[at] : 0.f;
+            i_next[j] = live ? wi[at] : 0.f;
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < part; k0 += KC) {
+#pragma unroll
+        for (int j = 0; j < U_PER; ++j) {
+            int e = threadIdx.x + j * 256;
+            u_tile[e % KC][e / KC] = u_next[j];
+        }
+#pragma unroll
+        for (int j = 0; j < W_PER; ++j) {
+            int e = threadIdx.x + j * 256;
+            a_tile[e % KC][e / KC] = a_next[j];
+            i_tile[e % KC][e / KC] = i_next[j];
         }
         __syncthreads();
+        if (k0 + KC < part) fetch(k0 + KC);
 #pragma unroll
         for (int k = 0; k < KC; ++k) {
             float un[TT];
