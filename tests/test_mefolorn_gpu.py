@@ -517,6 +517,25 @@ def test_batch_and_cut_change_nothing_in_32_bit(tmp_path):
     assert torch.equal(alone[0], cut[0])
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_passes_walked_from_their_record_agree_with_plain_passes(tmp_path, dtype):
+    """The same shape of step five times on other slots, pages and states: the first pass runs through the parts,
+    the second is recorded, the later ones are walked natively from the record; a mixed step likewise."""
+    from llm_b200.engine import Entry
+    config, weights, engine = _setup(tmp_path, "Q", dtype)
+    firsts = []
+    for again in range(5):
+        seqs = [random_tokens(n, config["vocab"], 100 * again + n) for n in (90, 33)]
+        slots = engine.acquire(2)
+        logits = engine.step([Entry(slots[0], seqs[0][:80], [0, 79]), Entry(slots[1], seqs[1][:30], [29])])
+        want = [plain.forward(config, weights, s) for s in seqs]
+        _check_logits(logits, torch.stack([want[0][0], want[0][79], want[1][29]]), dtype, ("prompt", again))
+        mixed = engine.step([Entry(slots[0], seqs[0][80:], [9]), Entry(slots[1], [seqs[1][30]], [0])])
+        _check_logits(mixed, torch.stack([want[0][89], want[1][30]]), dtype, ("mixed", again))
+        engine.release(slots)
+    assert engine.records_run >= 4
+
+
 def test_a_far_key_a_sink_and_a_lost_state_show_in_the_logits(tmp_path):
     """Changes that a fault would make, made on purpose in the plain model: each must move the logits by far
     more than the library differs from the unchanged plain model."""
