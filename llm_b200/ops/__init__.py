@@ -770,7 +770,7 @@ def linear(a, w, bias=None, out_dtype=None, residual=None, out=None, glu=False, 
 _attention_scratch: dict = {}      # outgrown buffers join `_retired` above
 
 
-def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
+def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int, wave: int = 296) -> int:
     """Into how many slices the keys of every sequence are cut for decode
     attention. Blocks are (slice, kv head, sequence) and two fit on an SM: the
     count is the largest power of two that keeps all blocks in one wave of
@@ -791,7 +791,7 @@ def decode_splits(n_seqs: int, n_kv_heads: int, max_len: int) -> int:
     pages = max(1, (max_len + PAGE - 1) // PAGE)
     floor_pages = max(1, 1 << max(0, (pages - 1).bit_length() - 1))      # the bucket is (floor, 2 floor] pages
     pairs = max(1, n_seqs * n_kv_heads)
-    want = 296 // pairs if pairs < 296 else min(4, max(1, floor_pages // 16))
+    want = wave // pairs if pairs < wave else min(4, max(1, floor_pages // 16))     # (wave: the blocks all SMs hold at once)
     splits = 1
     while splits * 2 <= want and splits * 2 <= 32:
         splits *= 2
@@ -916,16 +916,17 @@ def attention_replay_key(step, n_heads: int, n_kv_heads: int, window: int = 0):
     return (False, max(step.new_counts))
 
 
-def sigmoid_decode_splits(n_seqs: int, max_len: int, window: int) -> int:
+def sigmoid_decode_splits(n_seqs: int, max_len: int, window: int, mixed_width: int = 1024) -> int:
     """Slices of the decode kernel of the sigmoid attention (a block serves all heads of a sequence):
-    `decode_splits` for the keys a query sees at most."""
+    `decode_splits` for the keys a query sees at most. Two blocks share an SM where the mixed queries are
+    wide (`mixed_width` = kv heads x head size above 512), four where they are narrow."""
     seen = min(max_len, window + PAGE) if window > 0 else max_len
-    return decode_splits(n_seqs, 1, seen)
+    return decode_splits(n_seqs, 1, seen, wave=296 if mixed_width > 512 else 592)
 
 
 def sigmoid_attention_replay_key(step, spec):
     if step.decode:
-        return (True, sigmoid_decode_splits(step.n_seqs, step.max_len, spec.window))
+        return (True, sigmoid_decode_splits(step.n_seqs, step.max_len, spec.window, spec.n_kv_heads * spec.head_dim))
     return (False, max(step.new_counts))
 
 
@@ -954,7 +955,7 @@ def sigmoid_attention(q, k_cache, v_cache, block_table, ring_pages, tok_pos, tok
         decode, q.dtype, n_heads, n_kv_heads, dim, vdim, window, cu_seqlens is not None and seq_lens is not None,
         q.stride(0) % 2 == 0 and out.stride(0) % 2 == 0 and q.data_ptr() % 4 == 0 and out.data_ptr() % 4 == 0)
     if variant == "sigmoid_attention_decode":
-        splits = sigmoid_decode_splits(n, max_len, window)
+        splits = sigmoid_decode_splits(n, max_len, window, n_kv_heads * dim)
         need = (n * (16 if n_heads <= 16 else 32) * n_kv_heads * dim + 1) // 2 + (n * splits * n_heads * vdim if splits > 1 else 0)
         scratch = _attention_scratch.get(q.device)
         if scratch is None or scratch.numel() < need:
